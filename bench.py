@@ -1,0 +1,345 @@
+"""Benchmark of the ring-attention hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload (default `causal_32k`): bf16 causal self-attention, forward + backward, batch 2,
+16 heads, head dim 128, 32768 tokens in total, sharded evenly over the N GPUs of the ring
+(strong scaling), Q/K/V/dO ~ N(0,1) from a seeded generator, softmax scale 1/sqrt(128).
+One step = one ring forward + one ring backward.  Prints ONE JSON line on rank 0.
+
+`value` times the C-ABI ring calls with inputs resident in HBM; `e2e` times the public
+Python API (`ring_attention` + autograd backward) with inputs in pinned host memory, the
+host->device copies of q, k, v, dO and the device->host copies of out, dq, dk, dv inside
+the timed region.  FLOPs are counted exactly: 4d per visible (query, key) pair forward,
+10d backward.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: dtype, b, h, d, total tokens, mask
+    "causal_32k": dict(dtype="bf16", b=2, h=16, d=128, s=32768, mask="causal"),
+    "config1_fp32": dict(dtype="f32", b=1, h=4, d=64, s=1024, mask="causal"),
+    "causal_8k": dict(dtype="bf16", b=2, h=16, d=128, s=8192, mask="causal"),
+}
+METRIC = "ring_attention_fwd_bwd_tokens_per_s"
+
+
+def causal_pairs(s):
+    return s * (s + 1) // 2
+
+
+def flops(w, fwd=True, bwd=True):
+    per_pair = (4 * w["d"] if fwd else 0) + (10 * w["d"] if bwd else 0)
+    return w["b"] * w["h"] * causal_pairs(w["s"]) * per_pair
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(burst=p["bf16_tflops"], sustained=p["bf16_tflops_sustained"], hbm=p["hbm_gbs"], source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def cpu_baseline(w, nranks=4, budget_s=20.0):
+    """The reference's algorithm (ring.py:79-211) on the host cores through the oracle port:
+    a bounded sample of the workload (one batch element, a few heads, a shorter sequence),
+    converted to the metric's unit through the exact FLOP count."""
+    from oracle import oracle as O
+
+    cores = os.cpu_count() or 1
+    s, heads = 4096, 4
+    sample_flops = O.causal_flops(1, heads, s, w["d"])
+    t = O.timed_cpu_ring_causal(1, heads, s, w["d"], nranks)  # warm-up + size probe
+    reps = max(1, min(8, int(budget_s / max(t, 1e-3)) - 1))
+    ts = [O.timed_cpu_ring_causal(1, heads, s, w["d"], nranks, seed=i + 1) for i in range(reps)]
+    best = min(ts + [t])
+    flops_per_s = sample_flops / best
+    tokens_per_s = w["b"] * w["s"] / (flops(w) / flops_per_s)
+    return {
+        "value": tokens_per_s, "unit": "tokens/s", "cores": cores, "kind": "port",
+        "sample": f"oracle port (NumPy float32, BLAS on {cores} threads), causal fwd+bwd, b=1 h={heads} "
+                  f"S={s} d={w['d']} over {nranks} virtual ranks, best of {len(ts) + 1}: {best:.3f} s = "
+                  f"{flops_per_s / 1e9:.1f} GFLOP/s; scaled to the workload by its exact FLOP count",
+        "gflops": flops_per_s / 1e9,
+    }
+
+
+def run_reference(args, w):
+    """`--impl reference`: the reference's own CPU algorithm, timed on the host."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(w, budget_s=4.0)
+        if i >= args.warmup:
+            vals.append(base["value"])
+    v = sum(vals) / len(vals)
+    base["value"] = v
+    ms = w["b"] * w["s"] / v * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, w, args.gpus),
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference JAX path unavailable on this box (jax not installed, no network); "
+                "this is the CPU restatement of its algorithm; ms_per_step is the workload's time "
+                "extrapolated from the sample by FLOP count",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, w, n):
+    return {
+        "workload": f"{args.workload}: {w['dtype']} causal MHA fwd+bwd, batch {w['b']}, heads {w['h']}, "
+                    f"head_dim {w['d']}, total seq {w['s']} sharded evenly over {n} GPU(s)",
+        "global_batch": w["b"], "seq_len": w["s"], "heads": w["h"], "head_dim": w["d"],
+        "parallelism": f"sp{n}", "l2": "inputs larger than L2 (each of q,k,v,dO per rank exceeds 126 MB at N<=2; "
+                                      "an L2 flush runs between steps otherwise)",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="causal_32k", choices=list(WORKLOADS))
+    ap.add_argument("--block-impl", default="cuda", choices=["cuda", "simt", "tcgen05"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference(args, w)
+
+    import torch
+    import torch.distributed as dist
+
+    import ring_attention_b200 as ra
+    from ring_attention_b200 import _lib
+    from ring_attention_b200._lib import RaScoreMod, RaShape, RaTensor, check, lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    mesh = ra.Mesh((1, world), ("dp", "sp"))
+    ring = mesh.ring("sp")
+    ring.set_timing(True)
+    N = world
+    c = w["s"] // N
+    b, h, d = w["b"], w["h"], w["d"]
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    dcode = _lib.RA_DTYPE_BF16 if w["dtype"] == "bf16" else _lib.RA_DTYPE_F32
+    check(lib.ra_set_impl({"cuda": 0, "simt": 1, "tcgen05": 2}[args.block_impl]))
+
+    # synthetic inputs, pinned on the host (e2e) and resident on the device (value)
+    g = torch.Generator().manual_seed(1234 + rank)
+    host = [torch.randn((b, c, h, d), generator=g).to(dt).pin_memory() for _ in range(4)]
+    q, k, v, do = (t.cuda() for t in host)
+    pos = (torch.arange(c, dtype=torch.int32) + rank * c).expand(b, c).contiguous().cuda()
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    lse = torch.empty((b, h, c), dtype=torch.float32, device="cuda")
+    mod = RaScoreMod()
+    mod.kinds = _lib.RA_MOD_CAUSAL
+    mod.q_pos = mod.kv_pos = pos.data_ptr()
+    sh = RaShape(b, h, c, c, d, d, dcode, 1 / math.sqrt(d))
+    tv = lambda t: C.byref(RaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2)))
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if q.numel() * q.element_size() < (126 << 20) else None
+
+    def step():
+        check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
+        check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
+                              C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = lib.ra_launch_count()
+    fwd_block_ms, bwd_block_ms, exposed_ms = [], [], []
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    with ClockSampler(local) as clocks:
+        for i in range(args.steps):
+            if flush is not None:
+                flush.fill_(i)
+            evs[i][0].record()
+            check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
+            ms, n = ring.last_block_ms()  # synchronises on the call's end: device time of the block kernels
+            fwd_block_ms.append(ms / max(n, 1))
+            exposed_ms.append(ring.last_timing()[1])
+            check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
+                                  C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
+            evs[i][1].record()
+            ms, n = ring.last_block_ms()
+            bwd_block_ms.append(ms / max(n, 1))
+            exposed_ms[-1] += ring.last_timing()[1]
+        barrier()
+    launches = lib.ra_launch_count() - launches0
+    step_ms = sum(a.elapsed_time(b_) for a, b_ in evs) / args.steps
+    t = torch.tensor([step_ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms = float(t.item())
+    impl_used = {1: "simt", 2: "tcgen05"}.get(lib.ra_last_impl(), "?")
+
+    # end to end through the public API, host buffers in and out
+    e2e = None
+    if not args.no_e2e:
+        host_out = [torch.empty((b, c, h, d), dtype=dt).pin_memory() for _ in range(4)]
+        qkw = {"q_positions": pos}
+        kkw = {"kv_positions": pos}
+        sm = ra.ScoreMod(causal=True)
+
+        def e2e_step():
+            dq_, dk_, dv_, ddo = (t.cuda(non_blocking=True) for t in host)
+            dq_.requires_grad_(True)
+            dk_.requires_grad_(True)
+            dv_.requires_grad_(True)
+            o = ra.ring_attention(dq_, dk_, dv_, ring, bias_fn=sm, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
+                                  block_impl=args.block_impl)
+            o.backward(ddo)
+            for dst, src in zip(host_out, (o.detach(), dq_.grad, dk_.grad, dv_.grad)):
+                dst.copy_(src, non_blocking=True)
+
+        for _ in range(min(args.warmup, 2)):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nbytes = sum(x.numel() * x.element_size() for x in host)
+        e2e = {"value": b * w["s"] / (float(t.item()) * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": float(t.item())}
+
+    if rank == 0:
+        pk = peaks()
+        total_flops = flops(w)
+        tflops_gpu = total_flops / N / (step_ms * 1e-3) / 1e12
+        # dominant kernel: the backward block kernel.  Algorithmic FLOPs of one launch: the
+        # visible pairs of one (q shard, kv block) pair; averaged over the ring's steps.
+        bwd_flops_launch = flops(w, fwd=False) / N / N if N > 1 else flops(w, fwd=False)
+        fwd_flops_launch = flops(w, bwd=False) / N / N if N > 1 else flops(w, bwd=False)
+        bwd_ms = sum(bwd_block_ms) / len(bwd_block_ms)
+        fwd_ms = sum(fwd_block_ms) / len(fwd_block_ms)
+        achieved = bwd_flops_launch / (bwd_ms * 1e-3) / 1e12
+        peak = pk["sustained"] if bwd_ms > 5 else pk["burst"]
+        line = {
+            "metric": METRIC, "value": b * w["s"] / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": N,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": workload_config(args, w, N),
+            "tflops_per_gpu": tflops_gpu, "pct_bf16_peak": 100 * tflops_gpu / pk["sustained"],
+            "block_impl": impl_used,
+            "roofline": {
+                "bound": "tensor", "kernel": f"{impl_used} backward block", "achieved": achieved, "peak": peak,
+                "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if bwd_ms > 5 else 'burst'}",
+                "launch_ms": bwd_ms, "flops_per_launch": bwd_flops_launch,
+                "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
+            },
+            "exposed_comm_ms": sum(exposed_ms) / len(exposed_ms),
+            "exposed_comm_frac": (sum(exposed_ms) / len(exposed_ms)) / step_ms,
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if N == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

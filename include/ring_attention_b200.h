@@ -1,0 +1,193 @@
+/*
+ * ring_attention_b200 -- C ABI of the B200 (sm_100a) ring-attention engine.
+ *
+ * Every entry point is plain C: raw device pointers, sizes, strides and a CUDA stream
+ * passed as void*.  No exceptions cross this boundary.  Return value: 0 = ok;
+ * negative = argument error found on the host before anything was launched;
+ * positive = CUDA / NCCL error code class (see RA_ERR_*).  ra_last_error_string()
+ * gives the text for the calling thread's last failure.
+ *
+ * Tensors are addressed as [batch, length, heads, head_dim] with explicit element
+ * strides for batch, length and heads; head_dim is contiguous.  That covers both the
+ * reference's public layout "b l h d" (ring_attention/ring.py:80-82) and its internal
+ * layout "b h l d" (ring.py:96-98) without a copy.
+ *
+ * Citations "ring.py:NN", "ring_kernel.py:NN" refer to files under ring_attention/ of
+ * jondeaton/ring-attention-jax-pallas, the project this library is a drop-in for.
+ */
+#ifndef RING_ATTENTION_B200_H_
+#define RING_ATTENTION_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RA_VERSION 1
+
+/* element types of q, k, v, out, dout, dq, dk, dv */
+#define RA_DTYPE_F32 0
+#define RA_DTYPE_BF16 1
+
+/* error classes (positive return values) */
+#define RA_ERR_CUDA 1
+#define RA_ERR_NCCL 2
+#define RA_ERR_DEVICE_STATUS 3 /* a kernel reported a bounded wait that ran out */
+
+/* score-mod kinds, OR-ed into ra_score_mod_t.kinds */
+#define RA_MOD_CAUSAL 1u   /* keep kv_pos <= q_pos              (ring.py:394-397) */
+#define RA_MOD_SEGMENT 2u  /* keep q_seg == kv_seg              (ring.py:388-391) */
+#define RA_MOD_PREFIX 4u   /* keep (q_pre & kv_pre) | causal    (ring.py:399-406) */
+#define RA_MOD_ALIBI 8u    /* add -slope[h] * (q_pos - kv_pos)  (a bias_fn, ring.py:107) */
+#define RA_MOD_WINDOW 16u  /* keep q_pos - kv_pos < window      (a bias_fn, ring.py:107) */
+#define RA_MOD_DENSE 32u   /* add a materialised bias tile      (ring.py:60-61) */
+
+/* kernel families; RA_IMPL_AUTO picks tcgen05 whenever the shape allows it */
+#define RA_IMPL_AUTO 0
+#define RA_IMPL_SIMT 1    /* fp32 CUDA-core kernels: any shape, fp32-exact */
+#define RA_IMPL_TCGEN05 2 /* bf16 tensor-core kernels: fails if the shape does not fit */
+
+typedef struct ra_tensor {
+  void* ptr;        /* device pointer to element [0,0,0,0] */
+  int64_t stride_b; /* element strides; head_dim stride is 1 */
+  int64_t stride_l;
+  int64_t stride_h;
+} ra_tensor_t;
+
+typedef struct ra_shape {
+  int32_t b;   /* batch */
+  int32_t h;   /* heads (q, k and v share it: ring.py:59, 92-93) */
+  int32_t lq;  /* query rows in this block / shard */
+  int32_t lk;  /* key/value rows in this block / shard */
+  int32_t dk;  /* head dim of q and k */
+  int32_t dv;  /* head dim of v and out */
+  int32_t dtype;
+  float sm_scale; /* ring.py:287-288 default is 1/sqrt(dk); the caller resolves it */
+} ra_shape_t;
+
+/*
+ * Score modification: the compiled-in replacements for the reference's bias_fn
+ * (ring.py:107, 185-188, 376-409).  Per-token arrays are int32 [b, lq] / [b, lk],
+ * contiguous.  Any pointer whose kind bit is clear may be NULL.
+ */
+typedef struct ra_score_mod {
+  uint32_t kinds;
+  int32_t window;
+  const int32_t* q_pos;
+  const int32_t* kv_pos;
+  const int32_t* q_seg;
+  const int32_t* kv_seg;
+  const uint8_t* q_prefix;
+  const uint8_t* kv_prefix;
+  const float* alibi_slopes; /* [h] */
+  const float* bias;         /* dense fp32 tile, element (b,h,i,j) at b*sb + h*sh + i*sq + j */
+  int64_t bias_stride_b;
+  int64_t bias_stride_h; /* 0 broadcasts one tile over heads (ring.py:409) */
+  int64_t bias_stride_q;
+} ra_score_mod_t;
+
+/* ---- diagnostics ------------------------------------------------------------------ */
+int ra_version(void);
+const char* ra_last_error_string(void);
+/* Select the kernel family for later calls from this thread (RA_IMPL_*). */
+int ra_set_impl(int impl);
+/* Which family the last block call of this thread ran (RA_IMPL_SIMT / RA_IMPL_TCGEN05). */
+int ra_last_impl(void);
+/* Number of kernels this library has launched since load (all threads). */
+int64_t ra_launch_count(void);
+
+/* ---- block level: the reference's plug point ---------------------------------------
+ * ra_fwd_block replaces fwd_block / _fwd_block (ring_kernel.py:123-199, ring.py:58-76):
+ * one online-softmax update of the carried state (o, m, l) with one K/V block.
+ * o is fp32 [b,h,lq,dv] contiguous and un-normalised; m, l are fp32 [b,h,lq].
+ * The state is updated in place.  first != 0 means "state is (0, -inf, 0)" and the
+ * incoming buffers are not read (ring.py:124-126). mod may be NULL (no bias).
+ */
+int ra_fwd_block(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_t* k,
+                 const ra_tensor_t* v, const ra_score_mod_t* mod, float* o, float* m, float* l,
+                 int first, void* stream);
+
+/* out = o / l, L = m + log(l): ring.py:134-135.  out has the element type shape->dtype. */
+int ra_fwd_finalize(const ra_shape_t* shape, const float* o, const float* m, const float* l,
+                    const ra_tensor_t* out, float* lse, void* stream);
+
+/* delta = rowsum(out * dout) in fp32 [b,h,lq]: _precompute_delta, ring_kernel.py:387-409. */
+int ra_bwd_delta(const ra_shape_t* shape, const ra_tensor_t* out, const ra_tensor_t* dout,
+                 float* delta, void* stream);
+
+/* ra_bwd_block replaces bwd_block / _bwd_block (ring_kernel.py:202-297, ring.py:140-157):
+ * adds this block's contributions to fp32 accumulators dq [b,h,lq,dk], dk [b,h,lk,dk],
+ * dv [b,h,lk,dv] (contiguous; the caller zeroes them first, ring.py:198-200).
+ * lse and delta are fp32 [b,h,lq].
+ */
+int ra_bwd_block(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_t* k,
+                 const ra_tensor_t* v, const ra_score_mod_t* mod, const float* lse,
+                 const float* delta, const ra_tensor_t* dout, float* dq, float* dk, float* dv,
+                 void* stream);
+
+/* Convert a contiguous fp32 [b,h,len,d] accumulator to a strided tensor of `dtype`
+ * (the "b h l d -> b l h d" + cast at ring.py:208-210). */
+int ra_cast_from_f32(int32_t b, int32_t h, int32_t len, int32_t d, const float* src,
+                     const ra_tensor_t* dst, int32_t dtype, void* stream);
+
+/* ---- ring level -------------------------------------------------------------------
+ * A ring handle binds one GPU (the current device) to its place in a ring of nranks
+ * processes, one per GPU, and owns the K/V staging buffers, the fp32 carried state and
+ * the gradient accumulators.  It replaces the mesh axis named by axis_name together
+ * with lax.ppermute / lax.psum (ring.py:41-55, 101, 180).  nccl_id is the
+ * NCCL unique id shared by all ranks (ra_ring_unique_id on rank 0, then broadcast by
+ * the host program); it is ignored when nranks == 1.
+ */
+typedef struct ra_ring ra_ring_t;
+
+#define RA_UNIQUE_ID_BYTES 128
+int ra_ring_unique_id(uint8_t id[RA_UNIQUE_ID_BYTES]);
+int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE_ID_BYTES],
+                   ra_ring_t** ring);
+int ra_ring_destroy(ra_ring_t* ring);
+int ra_ring_rank(const ra_ring_t* ring);
+int ra_ring_size(const ra_ring_t* ring);
+
+/* Host-only schedule: which rank's K/V block this rank works on at step t
+ * ((rank - t) mod nranks: ring.py:54 with the scan of ring.py:128-132). */
+int ra_ring_source(int32_t rank, int32_t nranks, int32_t step);
+
+/* Fused ring forward: _ring_attention_fwd (ring.py:79-137).  q,k,v are this rank's
+ * shards; out gets this rank's rows in shape->dtype, lse gets L (fp32 [b,h,lq]).
+ * K/V (and the kv-side arrays of mod) of the other ranks are fetched over NVLink on a
+ * side stream into double buffers while the current block is computed.
+ * Every rank of the ring must make the same call with the same shape.
+ */
+int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
+                const ra_tensor_t* k, const ra_tensor_t* v, const ra_score_mod_t* mod,
+                const ra_tensor_t* out, float* lse, void* stream);
+
+/* Fused ring backward: _ring_attention_bwd (ring.py:160-211).  Q, dO, L, delta and dQ
+ * stay on their rank; K/V blocks are fetched as in the forward and each step's dK/dV
+ * contribution is sent to the block's owner, which sums them in fp32. */
+int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
+                const ra_tensor_t* k, const ra_tensor_t* v, const ra_tensor_t* out,
+                const float* lse, const ra_tensor_t* dout, const ra_score_mod_t* mod,
+                const ra_tensor_t* dq, const ra_tensor_t* dk, const ra_tensor_t* dv,
+                void* stream);
+
+/* Rotate caller-owned buffers one place round the ring (rank i -> rank i+1), the
+ * _rotate_block of ring.py:41-55, for the arbitrary-bias_fn path that loops on the host.
+ * Sends nbytes from each src[i] and receives into dst[i]; n buffers per call. */
+int ra_ring_rotate(ra_ring_t* ring, int32_t n, const void* const* src, void* const* dst,
+                   const int64_t* nbytes, void* stream);
+
+/* Milliseconds the compute stream spent blocked on transfers during the last
+ * ra_ring_fwd / ra_ring_bwd of this handle, and the total time of that call; both need
+ * ra_ring_set_timing(ring, 1) and synchronise the stream when read. */
+int ra_ring_set_timing(ra_ring_t* ring, int32_t on);
+int ra_ring_last_timing(ra_ring_t* ring, float* total_ms, float* exposed_comm_ms);
+/* Device time of the block kernels (ra_fwd_block / ra_bwd_block work) launched by the
+ * last ring call, summed over its steps, and how many there were (timing must be on). */
+int ra_ring_last_block_ms(ra_ring_t* ring, float* block_ms, int32_t* launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RING_ATTENTION_B200_H_ */

@@ -1,0 +1,405 @@
+"""CPU oracle for ring attention: TEST INFRASTRUCTURE ONLY.
+
+This file restates, in NumPy, the arithmetic of the reference project
+(jondeaton/ring-attention-jax-pallas).  It exists so that the CUDA engine can be
+checked against an independent statement of the same math, and so that a CPU
+baseline can be timed.  Nothing in the product path may import it: only the test
+suite, the smoke check and the benchmark's cpu-baseline / reference arm do.
+
+Pinning.  The reference stores no golden arrays; its tests draw inputs from
+`jax.random` (which cannot be regenerated without JAX) and assert one property:
+ring attention equals dense softmax attention and its gradients
+(ring_attention/ring_test.py:26-42, :97-98, :165-171, :273-274, :298-300, :378).
+JAX is not installable here, so outputs of the reference itself cannot be
+produced: in the byte-for-byte sense this oracle is "parity unpinned".  What is
+pinned (tests/test_oracle.py): (1) the ring emulation below equals the dense
+restatement of the reference test's `mha` at every shape the reference tests use,
+to 1e-12 in float64; (2) the dense restatement equals torch's CPU
+scaled_dot_product_attention and torch autograd gradients, an independent
+implementation; (3) the NaN pattern of fully masked rows equals the dense
+softmax's (ring_test.py:273).
+
+Each function cites the reference lines it follows.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Callable, Optional
+
+import numpy as np
+
+NEG_INF = -np.inf
+
+
+# --------------------------------------------------------------------------------------
+# Dense attention: ring_attention/ring_test.py:26-42 (`mha`), layout [b, l, h, d].
+# --------------------------------------------------------------------------------------
+def mha(q, k, v, bias=None, sm_scale=None, dtype=np.float64, return_lse=False):
+    """softmax(q k^T * scale + bias) v.  ring_test.py:26-42 uses scale 1/sqrt(dk)."""
+    q = np.asarray(q, dtype)
+    k = np.asarray(k, dtype)
+    v = np.asarray(v, dtype)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    z = np.einsum("bihd,bjhd->bhij", q, k) * dtype(sm_scale)
+    if bias is not None:
+        z = z + np.asarray(bias, dtype)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        m = np.max(z, axis=-1, keepdims=True)
+        p = np.exp(z - m)  # rows that are all -inf give exp(nan) = nan, like jax.nn.softmax
+        l = np.sum(p, axis=-1, keepdims=True)
+        a = p / l
+        out = np.einsum("bhij,bjhd->bihd", a, v)
+        if return_lse:
+            lse = (m + np.log(l))[..., 0]
+            return out, lse
+    return out
+
+
+def mha_grads(q, k, v, do, bias=None, sm_scale=None, dtype=np.float64):
+    """Gradients of sum(do * mha(q,k,v)) wrt q,k,v (the loss of ring_test.py:136,160)."""
+    q = np.asarray(q, dtype)
+    k = np.asarray(k, dtype)
+    v = np.asarray(v, dtype)
+    do = np.asarray(do, dtype)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    z = np.einsum("bihd,bjhd->bhij", q, k) * dtype(sm_scale)
+    if bias is not None:
+        z = z + np.asarray(bias, dtype)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        m = np.max(z, axis=-1, keepdims=True)
+        p = np.exp(z - m)
+        a = p / np.sum(p, axis=-1, keepdims=True)
+        out = np.einsum("bhij,bjhd->bihd", a, v)
+        dv = np.einsum("bhij,bihd->bjhd", a, do)
+        dp = np.einsum("bihd,bjhd->bhij", do, v)
+        delta = np.einsum("bihd,bihd->bhi", do, out)[..., None]
+        ds = a * (dp - delta) * dtype(sm_scale)
+        dq = np.einsum("bhij,bjhd->bihd", ds, k)
+        dk = np.einsum("bhij,bihd->bjhd", ds, q)
+    return dq, dk, dv
+
+
+# --------------------------------------------------------------------------------------
+# Block math, layout [b, h, l, d]: ring_attention/ring.py:58-76 and :140-157.
+# --------------------------------------------------------------------------------------
+def fwd_block(q, k, v, bias, o, m_prev, l, sm_scale):
+    """One online-softmax block update.  Follows ring.py:58-76 line by line."""
+    s = np.einsum("bhqd,bhkd->bhqk", q, k) * sm_scale  # ring.py:59
+    if bias is not None:
+        s = s + bias  # ring.py:60-61
+    with np.errstate(invalid="ignore"):
+        m = np.maximum(m_prev, np.max(s, axis=-1))  # ring.py:63
+        correction = np.exp(m_prev - m)  # ring.py:65
+        correction = np.where(np.isneginf(m) & np.isneginf(m_prev), 0, correction)  # :66
+        p = np.exp(s - m[..., None])  # ring.py:68
+        p = np.where(np.isneginf(m)[..., None], 0, p)  # ring.py:69
+    pv = np.einsum("bhqk,bhkd->bhqd", p, v)  # ring.py:70
+    o = o * correction[..., None] + pv  # ring.py:72
+    l = correction * l + np.sum(p, axis=-1)  # ring.py:75
+    return o, m, l
+
+
+def bwd_block(q, k, v, bias, o, L, do, sm_scale):
+    """Block VJP.  Follows ring.py:140-157."""
+    s = np.einsum("bhqd,bhkd->bhqk", q, k) * sm_scale  # ring.py:142
+    if bias is not None:
+        s = s + bias
+    with np.errstate(invalid="ignore"):
+        p = np.exp(s - L[..., None])  # ring.py:146
+        dv = np.einsum("bhqk,bhqd->bhkd", p, do)  # ring.py:148
+        dp = np.einsum("bhqd,bhkd->bhqk", do, v)  # ring.py:150
+        delta = np.sum(do * o, axis=-1, keepdims=True)  # ring.py:151
+        ds = p * (dp - delta) * sm_scale  # ring.py:152
+        dq = np.einsum("bhqk,bhkd->bhqd", ds, k)  # ring.py:154
+        dk = np.einsum("bhqk,bhqd->bhkd", ds, q)  # ring.py:155
+    return dq, dk, dv
+
+
+def finalize(o, m, l):
+    """out = o / l ; L = m + log l.  ring.py:134-135."""
+    with np.errstate(invalid="ignore", divide="ignore"):
+        return o / l[..., None], m + np.log(l)
+
+
+# --------------------------------------------------------------------------------------
+# Ring schedule over N virtual ranks: ring.py:79-137 (forward), :160-211 (backward),
+# rotation ring.py:41-55 (rank i sends to rank (i+1) % N).
+# --------------------------------------------------------------------------------------
+def _rotate(blocks):
+    """Cyclic +1 shift over the rank axis: what rank i held is now on rank i+1 (ring.py:51-55)."""
+    return [blocks[(r - 1) % len(blocks)] for r in range(len(blocks))]
+
+
+def _bhld(x):
+    return np.ascontiguousarray(np.transpose(x, (0, 2, 1, 3)))
+
+
+def ring_attention_fwd(
+    q_shards,
+    k_shards,
+    v_shards,
+    bias_fn: Optional[Callable] = None,
+    q_kwargs=None,
+    kv_kwargs=None,
+    sm_scale=None,
+    dtype=np.float64,
+    block_fn=fwd_block,
+):
+    """Forward over N = len(q_shards) virtual ranks; shards are [b, c, h, d] (ring.py:80-82).
+
+    q_kwargs / kv_kwargs: per-rank lists of dicts of per-token arrays [b, c] that travel
+    with the queries / keys (ring.py:107,120).  Returns per-rank (out [b,c,h,dv], L [b,h,c]).
+    """
+    n = len(q_shards)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q_shards[0].shape[-1])  # ring.py:287-288
+    q_kwargs = q_kwargs or [{} for _ in range(n)]
+    kv_kwargs = kv_kwargs or [{} for _ in range(n)]
+    q = [_bhld(np.asarray(x, dtype)) for x in q_shards]  # ring.py:96-98
+    k = [_bhld(np.asarray(x, dtype)) for x in k_shards]
+    v = [_bhld(np.asarray(x, dtype)) for x in v_shards]
+    kvk = list(kv_kwargs)
+    o = [np.zeros(q[r].shape[:3] + (v[r].shape[-1],), dtype) for r in range(n)]  # ring.py:124
+    l = [np.zeros(q[r].shape[:3], dtype) for r in range(n)]  # ring.py:125
+    m = [np.full(q[r].shape[:3], NEG_INF, dtype) for r in range(n)]  # ring.py:126
+    for _ in range(n):  # ring.py:128-132
+        for r in range(n):
+            bias = bias_fn(**q_kwargs[r], **kvk[r]) if bias_fn is not None else None
+            o[r], m[r], l[r] = block_fn(q[r], k[r], v[r], bias, o[r], m[r], l[r], sm_scale)
+        k, v, kvk = _rotate(k), _rotate(v), _rotate(kvk)  # ring.py:120
+    outs, lses = [], []
+    for r in range(n):
+        out, L = finalize(o[r], m[r], l[r])
+        outs.append(np.transpose(out, (0, 2, 1, 3)))  # ring.py:137
+        lses.append(L)
+    return outs, lses
+
+
+def ring_attention_bwd(
+    q_shards,
+    k_shards,
+    v_shards,
+    out_shards,
+    lse_shards,
+    do_shards,
+    bias_fn=None,
+    q_kwargs=None,
+    kv_kwargs=None,
+    sm_scale=None,
+    dtype=np.float64,
+    block_fn=bwd_block,
+):
+    """Backward over N virtual ranks: K,V,dK,dV stay, the query bundle travels (ring.py:183-206)."""
+    n = len(q_shards)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q_shards[0].shape[-1])
+    q_kwargs = q_kwargs or [{} for _ in range(n)]
+    kv_kwargs = kv_kwargs or [{} for _ in range(n)]
+    q = [_bhld(np.asarray(x, dtype)) for x in q_shards]
+    k = [_bhld(np.asarray(x, dtype)) for x in k_shards]
+    v = [_bhld(np.asarray(x, dtype)) for x in v_shards]
+    o = [_bhld(np.asarray(x, dtype)) for x in out_shards]
+    do = [_bhld(np.asarray(x, dtype)) for x in do_shards]  # ring.py:173
+    L = [np.asarray(x, dtype) for x in lse_shards]
+    qk = list(q_kwargs)
+    dq = [np.zeros_like(x) for x in q]  # ring.py:198-200
+    dk = [np.zeros_like(x) for x in k]
+    dv = [np.zeros_like(x) for x in v]
+    for _ in range(n):  # ring.py:202-206
+        for r in range(n):
+            bias = bias_fn(**qk[r], **kv_kwargs[r]) if bias_fn is not None else None
+            dq_, dk_, dv_ = block_fn(q[r], k[r], v[r], bias, o[r], L[r], do[r], sm_scale)
+            dq[r] = dq[r] + dq_  # ring.py:191-193
+            dk[r] = dk[r] + dk_
+            dv[r] = dv[r] + dv_
+        q, o, dq, do, L, qk = (_rotate(x) for x in (q, o, dq, do, L, qk))  # ring.py:195
+    t = lambda xs: [np.transpose(x, (0, 2, 1, 3)) for x in xs]  # ring.py:208-210
+    return t(dq), t(dk), t(dv)
+
+
+# --------------------------------------------------------------------------------------
+# Bias builders.
+# --------------------------------------------------------------------------------------
+def self_attention_bias(
+    causal: bool,
+    q_segment_ids=None,
+    kv_segment_ids=None,
+    q_positions=None,
+    kv_positions=None,
+    q_prefix_mask=None,
+    kv_prefix_mask=None,
+):
+    """The block bias of ring_self_attention: ring.py:376-409.  Returns [b, 1, lq, lk]."""
+    mask = np.array(True)
+    if q_segment_ids is not None:
+        mask = mask & (q_segment_ids[:, :, None] == kv_segment_ids[:, None, :])  # ring.py:390-391
+    if causal:
+        mask = mask & (kv_positions[:, None, :] <= q_positions[:, :, None])  # ring.py:396-397
+    elif q_prefix_mask is not None:
+        pre = q_prefix_mask[:, :, None].astype(bool) & kv_prefix_mask[:, None, :].astype(bool)
+        cau = kv_positions[:, None, :] <= q_positions[:, :, None]
+        mask = mask & (pre | cau)  # ring.py:404-406
+    bias = np.where(mask, 0.0, NEG_INF)  # ring.py:408
+    return bias[:, None, :, :]  # ring.py:409
+
+
+def score_mod_bias(
+    b,
+    h,
+    q_positions=None,
+    kv_positions=None,
+    q_segment_ids=None,
+    kv_segment_ids=None,
+    q_prefix_mask=None,
+    kv_prefix_mask=None,
+    causal=False,
+    alibi_slopes=None,
+    window=0,
+):
+    """Dense [b, h, lq, lk] bias for the engine's compiled-in score-mod variants.
+
+    causal / segment / prefix follow ring.py:386-408.  ALiBi adds
+    -slope[h] * (q_pos - kv_pos); a sliding window of W keeps pairs with
+    q_pos - kv_pos < W (combined with causal this is 0 <= q_pos - kv_pos < W).
+    These two have no counterpart in the reference other than through a user bias_fn
+    (ring.py:107); they are defined here as that bias_fn would compute them.
+    """
+    lq = (q_positions if q_positions is not None else q_segment_ids).shape[1]
+    lk = (kv_positions if kv_positions is not None else kv_segment_ids).shape[1]
+    mask = np.ones((b, 1, lq, lk), bool)
+    if q_segment_ids is not None:
+        mask &= (q_segment_ids[:, :, None] == kv_segment_ids[:, None, :])[:, None]
+    rel = None
+    if q_positions is not None:
+        rel = (q_positions[:, :, None].astype(np.int64) - kv_positions[:, None, :].astype(np.int64))[:, None]
+    if causal:
+        mask &= rel >= 0
+    elif q_prefix_mask is not None:
+        pre = (q_prefix_mask[:, :, None].astype(bool) & kv_prefix_mask[:, None, :].astype(bool))[:, None]
+        mask &= pre | (rel >= 0)
+    if window:
+        mask &= rel < window
+    bias = np.zeros((b, h, lq, lk), np.float64)
+    if alibi_slopes is not None:
+        bias = bias - np.asarray(alibi_slopes, np.float64)[None, :, None, None] * rel
+    return np.where(mask, bias, NEG_INF)
+
+
+def alibi_slopes(h, zero_based=False):
+    """Slopes 2^(-8(i+1)/h) for head i (the usual ALiBi convention); zero_based gives 2^(-8i/h)."""
+    i = np.arange(h, dtype=np.float64)
+    return 2.0 ** (-8.0 * (i if zero_based else i + 1) / h)
+
+
+def pack_documents(total_len, lo, hi, seed):
+    """Segment ids [total_len] from document lengths drawn uniformly in [lo, hi] until full."""
+    rng = np.random.default_rng(seed)
+    ids = np.empty(total_len, np.int32)
+    pos, doc = 0, 0
+    lens = []
+    while pos < total_len:
+        n = int(rng.integers(lo, hi + 1))
+        n = min(n, total_len - pos)
+        ids[pos : pos + n] = doc
+        lens.append(n)
+        pos += n
+        doc += 1
+    return ids, np.asarray(lens, np.int64)
+
+
+# --------------------------------------------------------------------------------------
+# Exact pair counters for FLOP accounting (pairs * 4d fwd, * 10d bwd).
+# --------------------------------------------------------------------------------------
+def pairs_causal(s):
+    return s * (s + 1) // 2
+
+
+def pairs_documents(lens):
+    lens = np.asarray(lens, np.int64)
+    return int(np.sum(lens * (lens + 1) // 2))
+
+
+def pairs_window(s, w):
+    i = np.arange(s, dtype=np.int64)
+    return int(np.sum(np.minimum(i + 1, w)))
+
+
+def pairs_from_bias(bias):
+    return int(np.sum(~np.isneginf(bias)))
+
+
+# --------------------------------------------------------------------------------------
+# Convenience: split a global [b, S, ...] array into N contiguous shards on axis 1.
+# --------------------------------------------------------------------------------------
+def shard(x, n):
+    return [np.ascontiguousarray(s) for s in np.split(np.asarray(x), n, axis=1)]
+
+
+def unshard(xs, axis=1):
+    return np.concatenate(xs, axis=axis)
+
+
+# --------------------------------------------------------------------------------------
+# BLAS-backed restatement of the same block math, for the TIMED CPU baseline only.
+# np.einsum above does not call a threaded GEMM; np.matmul does, so this is the form that
+# uses all host cores.  tests/test_oracle.py checks it against fwd_block / bwd_block.
+# --------------------------------------------------------------------------------------
+def fwd_block_mm(q, k, v, bias, o, m_prev, l, sm_scale):
+    """ring.py:58-76 with batched GEMMs."""
+    s = np.matmul(q, np.swapaxes(k, -1, -2)) * q.dtype.type(sm_scale)
+    if bias is not None:
+        s += bias
+    with np.errstate(invalid="ignore"):
+        m = np.maximum(m_prev, np.max(s, axis=-1))
+        correction = np.exp(m_prev - m)
+        correction = np.where(np.isneginf(m) & np.isneginf(m_prev), 0, correction).astype(q.dtype)
+        np.subtract(s, m[..., None], out=s)
+        np.exp(s, out=s)
+        p = np.where(np.isneginf(m)[..., None], 0, s).astype(q.dtype)
+    o = o * correction[..., None] + np.matmul(p, v)
+    l = correction * l + np.sum(p, axis=-1)
+    return o, m, l
+
+
+def bwd_block_mm(q, k, v, bias, o, L, do, sm_scale):
+    """ring.py:140-157 with batched GEMMs."""
+    s = np.matmul(q, np.swapaxes(k, -1, -2)) * q.dtype.type(sm_scale)
+    if bias is not None:
+        s += bias
+    with np.errstate(invalid="ignore"):
+        p = np.exp(s - L[..., None])
+        dv = np.matmul(np.swapaxes(p, -1, -2), do)
+        dp = np.matmul(do, np.swapaxes(v, -1, -2))
+        delta = np.sum(do * o, keepdims=True, axis=-1)
+        ds = p * (dp - delta) * q.dtype.type(sm_scale)
+        dq = np.matmul(ds, k)
+        dk = np.matmul(np.swapaxes(ds, -1, -2), q)
+    return dq, dk, dv
+
+
+def causal_flops(b, h, s, d, fwd=True, bwd=True):
+    """Algorithmic FLOPs of causal attention: 4d per visible pair forward, 10d backward."""
+    per_pair = (4 * d if fwd else 0) + (10 * d if bwd else 0)
+    return b * h * pairs_causal(s) * per_pair
+
+
+def timed_cpu_ring_causal(b, h, s, d, nranks, seed=0, dtype=np.float32):
+    """One forward+backward of causal ring attention over `nranks` virtual ranks on the
+    host (the reference's algorithm, ring.py:79-211, BLAS block math).  Returns seconds."""
+    import time
+
+    rng = np.random.default_rng(seed)
+    mk = lambda: rng.standard_normal((b, s, h, d)).astype(dtype)
+    q, k, v, do = mk(), mk(), mk(), mk()
+    pos = np.broadcast_to(np.arange(s, dtype=np.int32), (b, s))
+    fn = lambda **kw: self_attention_bias(True, **kw).astype(dtype)
+    qk = [{"q_positions": p} for p in shard(pos, nranks)]
+    kk = [{"kv_positions": p} for p in shard(pos, nranks)]
+    qs, ks, vs, dos = (shard(x, nranks) for x in (q, k, v, do))
+    t0 = time.perf_counter()
+    outs, lses = ring_attention_fwd(qs, ks, vs, fn, qk, kk, dtype=dtype, block_fn=fwd_block_mm)
+    ring_attention_bwd(qs, ks, vs, outs, lses, dos, fn, qk, kk, dtype=dtype, block_fn=bwd_block_mm)
+    return time.perf_counter() - t0

@@ -1,0 +1,13 @@
+"""B200-native ring attention behind the API of jondeaton/ring-attention-jax-pallas.
+
+`ring_attention` and `ring_self_attention` are what ring_attention/__init__.py:3 of the
+reference re-exports; the rest is the host plumbing a one-process-per-GPU program needs.
+"""
+from ._lib import LIB_PATH, RingAttentionError
+from .mesh import Mesh, PartitionSpec, Ring
+from .ring import ScoreMod, bwd_block, fwd_block, ring_attention, ring_self_attention
+
+__all__ = [
+    "ring_attention", "ring_self_attention", "fwd_block", "bwd_block", "ScoreMod",
+    "Mesh", "PartitionSpec", "Ring", "RingAttentionError", "LIB_PATH",
+]

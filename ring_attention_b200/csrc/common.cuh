@@ -1,0 +1,99 @@
+// Internal parameter blocks shared by the host dispatcher and the kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ring_attention_b200.h"
+
+namespace ra {
+
+struct TensorView {
+  const void* ptr;
+  int64_t sb, sl, sh;  // element strides of batch, length, heads; head_dim stride is 1
+};
+
+struct ModParams {
+  uint32_t kinds;
+  int32_t window;
+  const int32_t* q_pos;
+  const int32_t* kv_pos;
+  const int32_t* q_seg;
+  const int32_t* kv_seg;
+  const uint8_t* q_pre;
+  const uint8_t* kv_pre;
+  const float* slopes;
+  const float* bias;
+  int64_t bsb, bsh, bsq;
+};
+
+struct FwdParams {
+  TensorView q, k, v;
+  ModParams mod;
+  float* o;  // [b,h,lq,dv] fp32, un-normalised
+  float* m;  // [b,h,lq]
+  float* l;  // [b,h,lq]
+  int32_t b, h, lq, lk, dk, dv;
+  float scale;
+  int32_t first;
+};
+
+struct BwdParams {
+  TensorView q, k, v, dout;
+  ModParams mod;
+  const float* lse;    // [b,h,lq]
+  const float* delta;  // [b,h,lq]
+  float* dq;           // [b,h,lq,dk] fp32, accumulated with atomics
+  float* dk;           // [b,h,lk,dk] fp32, += per call
+  float* dv;           // [b,h,lk,dv] fp32, += per call
+  int32_t b, h, lq, lk, dk_dim, dv_dim;
+  float scale;
+};
+
+// Launchers implemented in the .cu files.  Each returns a cudaError_t.
+cudaError_t simt_fwd_block(const FwdParams& p, int dtype, cudaStream_t s);
+cudaError_t simt_bwd_block(const BwdParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_finalize(int b, int h, int lq, int dv, const float* o, const float* m,
+                            const float* l, TensorView out, int dtype, float* lse, cudaStream_t s);
+cudaError_t launch_delta(int b, int h, int lq, int dv, TensorView out, TensorView dout, int dtype,
+                         float* delta, cudaStream_t s);
+cudaError_t launch_cast_from_f32(int b, int h, int len, int d, const float* src, TensorView dst,
+                                 int dtype, cudaStream_t s);
+cudaError_t launch_add_f32(float* dst, const float* src, int64_t n, cudaStream_t s);
+
+void count_launch(int n = 1);
+
+// One (query, key) score after scaling: mask + bias exactly as the reference's bias_fn
+// variants would produce it (ring.py:386-408), -inf where the pair is masked.
+struct ModRow {
+  int32_t pos, seg;
+  bool pre;
+};
+
+__device__ __forceinline__ float apply_mod(float s, uint32_t kinds, int32_t window, float slope,
+                                           int32_t qpos, int32_t qseg, bool qpre, int32_t kpos,
+                                           int32_t kseg, bool kpre) {
+  bool vis = true;
+  if (kinds & RA_MOD_SEGMENT) vis = vis && (qseg == kseg);
+  if (kinds & RA_MOD_CAUSAL) {
+    vis = vis && (kpos <= qpos);
+  } else if (kinds & RA_MOD_PREFIX) {
+    vis = vis && ((qpre && kpre) || (kpos <= qpos));
+  }
+  if (kinds & RA_MOD_WINDOW) vis = vis && ((qpos - kpos) < window);
+  if (kinds & RA_MOD_ALIBI) s -= slope * (float)(qpos - kpos);
+  return vis ? s : -INFINITY;
+}
+
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T* p);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const float* p) {
+  return *p;
+}
+template <>
+__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+
+}  // namespace ra

@@ -1,0 +1,82 @@
+"""Writes tests/golden/*.npz from the CPU oracle (oracle/oracle.py, float64).
+
+The reference project stores no golden arrays and cannot be run here (JAX is not
+installable), so these fixtures pin the ORACLE: they freeze today's float64 answers so
+that a later edit of the oracle, or of the engine, that changes results is caught.
+Inputs are not stored; `inputs(case)` below regenerates them from a seeded NumPy PCG64
+stream.  Run from the repository root:  python tests/golden/make_golden.py
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import oracle as O  # noqa: E402
+
+# name -> (seed, b, q_len, kv_len, h, d, nranks, mask)
+# shapes: ring_test.py:49-52 (forward), :105-110 (backward), :323-328 (self attention),
+# and the CPU-runnable benchmark configuration (b1 h4 S1024 d64, 4 ranks, causal).
+CASES = {
+    "tiny_cross": (0, 2, 24, 16, 1, 2, 8, "none"),
+    "cross_128_64": (1, 2, 128, 64, 4, 64, 8, "none"),
+    "cross_64_512": (2, 2, 64, 512, 4, 16, 8, "none"),
+    "segments_128_64": (1, 2, 128, 64, 4, 64, 8, "segments"),
+    "self_causal_seg_512": (2, 2, 512, 512, 4, 16, 8, "causal+segments"),
+    "config1_causal_1024": (0, 1, 1024, 1024, 4, 64, 4, "causal"),
+}
+
+
+def inputs(name):
+    seed, b, lq, lk, h, d, n, mask = CASES[name]
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((b, lq, h, d)).astype(np.float32)
+    k = rng.standard_normal((b, lk, h, d)).astype(np.float32)
+    v = rng.standard_normal((b, lk, h, d)).astype(np.float32)
+    do = rng.standard_normal((b, lq, h, d)).astype(np.float32)
+    extra = {}
+    if mask == "segments":  # ring_test.py:203-208: independent ids in [0, q_len // 5)
+        extra["q_seg"] = rng.integers(0, lq // 5, (b, lq)).astype(np.int32)
+        extra["kv_seg"] = rng.integers(0, lq // 5, (b, lk)).astype(np.int32)
+    if mask == "causal+segments":  # ring_test.py:347-350
+        extra["q_seg"] = extra["kv_seg"] = rng.integers(0, 5, (b, lq)).astype(np.int32)
+    if "causal" in mask:
+        extra["q_pos"] = np.broadcast_to(np.arange(lq, dtype=np.int32), (b, lq)).copy()
+        extra["kv_pos"] = np.broadcast_to(np.arange(lk, dtype=np.int32), (b, lk)).copy()
+    return q, k, v, do, extra
+
+
+def dense_bias(name, extra):
+    seed, b, lq, lk, h, d, n, mask = CASES[name]
+    if mask == "none":
+        return None
+    return O.score_mod_bias(b, h, q_positions=extra.get("q_pos"), kv_positions=extra.get("kv_pos"),
+                            q_segment_ids=extra.get("q_seg"), kv_segment_ids=extra.get("kv_seg"),
+                            causal="causal" in mask)
+
+
+def answers(name):
+    q, k, v, do, extra = inputs(name)
+    bias = dense_bias(name, extra)
+    out, lse = O.mha(q, k, v, bias, return_lse=True)
+    dq, dk, dv = O.mha_grads(q, k, v, do, bias)
+    return {"out": out, "lse": lse, "dq": dq, "dk": dk, "dv": dv}
+
+
+def main():
+    for name in CASES:
+        ans = answers(name)
+        if name.startswith("config1"):  # keep the file small: every 16th row
+            ans = {k2: (a[:, ::16] if k2 != "lse" else a[:, :, ::16]) for k2, a in ans.items()}
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **{k2: a.astype(np.float32) for k2, a in ans.items()})
+        print(path, os.path.getsize(path))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,129 @@
+"""CPU tests of the host side: the C-ABI library loads and exports what the header
+declares, argument errors are reported before any launch, and the schedule / mesh /
+score-mod helpers agree with the oracle.  No compute call is made here."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from ring_attention_b200 import Mesh, ScoreMod, _lib
+from ring_attention_b200._lib import RaScoreMod, RaShape, RaTensor, lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        text = open(os.path.join(inc, f)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(ra_[a-z0-9_]+)\s*\(", text))
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    declared = _header_symbols()
+    assert declared, "no declarations found"
+    raw = C.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(raw, name), f"{name} is declared in include/ but not exported"
+    assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
+    assert lib.ra_version() == 1
+
+
+def _shape(**kw):
+    d = dict(b=1, h=1, lq=4, lk=4, dk=8, dv=8, dtype=0, sm_scale=1.0)
+    d.update(kw)
+    return RaShape(*[d[k] for k in ("b", "h", "lq", "lk", "dk", "dv", "dtype", "sm_scale")])
+
+
+def _err():
+    return lib.ra_last_error_string().decode()
+
+
+def test_argument_errors_are_negative_and_explained():
+    t = RaTensor(0x1000, 1, 1, 1)
+    one = C.c_void_p(0x1000)
+    args = (C.byref(t), C.byref(t), C.byref(t))
+    assert lib.ra_fwd_block(None, *args, None, one, one, one, 1, None) == -1
+    rc = lib.ra_fwd_block(C.byref(_shape(lq=0)), *args, None, one, one, one, 1, None)
+    assert rc == -2 and "lq" in _err()
+    assert lib.ra_fwd_block(C.byref(_shape(dk=512)), *args, None, one, one, one, 1, None) == -3
+    assert lib.ra_fwd_block(C.byref(_shape(dtype=7)), *args, None, one, one, one, 1, None) == -4
+    assert lib.ra_fwd_block(C.byref(_shape()), None, args[1], args[2], None, one, one, one, 1, None) == -6
+    assert lib.ra_fwd_block(C.byref(_shape()), *args, None, None, one, one, 1, None) == -6
+    # score-mod combinations ring_self_attention refuses (ring.py:368-374)
+    m = RaScoreMod()
+    m.kinds = _lib.RA_MOD_CAUSAL | _lib.RA_MOD_PREFIX
+    assert lib.ra_fwd_block(C.byref(_shape()), *args, C.byref(m), one, one, one, 1, None) == -8
+    m.kinds = _lib.RA_MOD_CAUSAL  # positions missing
+    rc = lib.ra_fwd_block(C.byref(_shape()), *args, C.byref(m), one, one, one, 1, None)
+    assert rc == -9 and "positions" in _err()
+    m.kinds = _lib.RA_MOD_SEGMENT
+    assert lib.ra_fwd_block(C.byref(_shape()), *args, C.byref(m), one, one, one, 1, None) == -10
+    m.kinds = 1 << 12
+    assert lib.ra_fwd_block(C.byref(_shape()), *args, C.byref(m), one, one, one, 1, None) == -7
+    assert lib.ra_set_impl(9) == -21
+    assert lib.ra_set_impl(_lib.RA_IMPL_AUTO) == 0
+    assert lib.ra_ring_source(0, 0, 0) < 0
+    assert lib.ra_ring_fwd(None, C.byref(_shape()), *args, None, C.byref(t), one, None) == -30
+
+
+def test_ring_source_matches_reference_rotation():
+    """After t rotations i -> i+1 (ring.py:54) rank r holds the block of rank (r - t) mod N."""
+    for n in (1, 2, 3, 4, 8):
+        held = list(range(n))
+        for t in range(n):
+            for r in range(n):
+                assert lib.ra_ring_source(r, n, t) == held[r]
+            held = [held[(r - 1) % n] for r in range(n)]
+
+
+def test_mesh_coordinates():
+    assert Mesh.coords_of(5, (2, 4)) == (1, 1)
+    assert Mesh.axis_ranks(5, 1, (2, 4)) == [4, 5, 6, 7]
+    assert Mesh.axis_ranks(5, 0, (2, 4)) == [1, 5]
+    assert Mesh.axis_ranks(3, 1, (1, 8)) == list(range(8))  # ring_test.py:60-65
+
+
+@pytest.mark.parametrize("causal,seg,prefix,alibi,window", [
+    (True, False, False, False, 0), (True, True, False, False, 0), (False, True, False, False, 0),
+    (False, True, True, False, 0), (True, False, False, True, 7), (False, False, False, False, 5),
+])
+def test_score_mod_dense_form_matches_oracle(causal, seg, prefix, alibi, window):
+    rng = np.random.default_rng(0)
+    b, h, lq, lk = 2, 3, 20, 28
+    qpos = rng.integers(0, 40, (b, lq)).astype(np.int32)
+    kpos = rng.integers(0, 40, (b, lk)).astype(np.int32)
+    qseg = rng.integers(0, 3, (b, lq)).astype(np.int32) if seg else None
+    kseg = rng.integers(0, 3, (b, lk)).astype(np.int32) if seg else None
+    qpre = rng.integers(0, 2, (b, lq)).astype(bool) if prefix else None
+    kpre = rng.integers(0, 2, (b, lk)).astype(bool) if prefix else None
+    slopes = O.alibi_slopes(h) if alibi else None
+    want = O.score_mod_bias(b, h, qpos, kpos, qseg, kseg, qpre, kpre, causal, slopes, window)
+    T = lambda a: None if a is None else torch.from_numpy(a)
+    mod = ScoreMod(causal=causal, alibi_slopes=T(slopes), window=window)
+    got = mod(q_segment_ids=T(qseg), kv_segment_ids=T(kseg), q_positions=T(qpos), kv_positions=T(kpos),
+              q_prefix_mask=T(qpre), kv_prefix_mask=T(kpre)).numpy()
+    np.testing.assert_allclose(np.broadcast_to(got, want.shape), want, rtol=1e-6)
+    kinds = mod.kinds({"q_segment_ids": qseg, "q_prefix_mask": qpre}, {})
+    assert bool(kinds & _lib.RA_MOD_CAUSAL) == causal
+    assert bool(kinds & _lib.RA_MOD_SEGMENT) == seg
+    assert bool(kinds & _lib.RA_MOD_PREFIX) == (prefix and not causal)
+
+
+def test_api_refuses_cpu_tensors_and_unknown_impl():
+    import ring_attention_b200 as ra
+
+    q = torch.zeros(1, 4, 1, 8)
+    with pytest.raises(ValueError):
+        ra.ring_attention(q, q, q, "sp", block_impl="numpy")  # ring.py:311-312
+    with pytest.raises(ra.RingAttentionError):
+        ra.ring_attention(q, q, q, "sp")
+    with pytest.raises(AssertionError):
+        ra.ring_self_attention(q, q, q, None, ("dp", "sp", None), causal=True)  # ring.py:368-370
