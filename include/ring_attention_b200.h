@@ -97,6 +97,12 @@ int ra_last_impl(void);
 /* Number of kernels this library has launched since load (all threads). */
 int64_t ra_launch_count(void);
 
+/* Synchronises the current device, then reads and clears its kernel status word.  Every
+ * wait inside the tcgen05 kernels (on an mbarrier fed by TMA, by the tensor pipe or by
+ * other warps) is bounded; a wait that runs out sets a bit, the kernel drains and returns,
+ * and this call then returns RA_ERR_DEVICE_STATUS with the bits in *bits (else 0). */
+int ra_device_status(uint32_t* bits);
+
 /* ---- block level: the reference's plug point ---------------------------------------
  * ra_fwd_block replaces fwd_block / _fwd_block (ring_kernel.py:123-199, ring.py:58-76):
  * one online-softmax update of the carried state (o, m, l) with one K/V block.

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "ra_set_impl": (C.c_int, [C.c_int]),
     "ra_last_impl": (C.c_int, []),
     "ra_launch_count": (C.c_int64, []),
+    "ra_device_status": (C.c_int, [_P(C.c_uint32)]),
     "ra_fwd_block": (C.c_int, [_P(RaShape), _P(RaTensor), _P(RaTensor), _P(RaTensor), _P(RaScoreMod),
                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "ra_fwd_finalize": (C.c_int, [_P(RaShape), C.c_void_p, C.c_void_p, C.c_void_p, _P(RaTensor),

@@ -1,7 +1,510 @@
-// placeholder until the tcgen05 forward lands
-#include "common.cuh"
+// tcgen05 forward block kernel for sm_100a: one online-softmax update of the carried
+// state (o, m, l) with one K/V block, bf16 inputs, head dim 64 or 128.  It computes what
+// fwd_block / _fwd_kernel of the reference compute (ring_attention/ring_kernel.py:41-199,
+// math of ring.py:58-76).
+//
+// One CTA owns two 128-row query tiles and walks the K/V tiles of the block:
+//   warp 8   : TMA producer   (Q once, then K and V tiles into 2-stage rings)
+//   warp 9   : MMA issuer     (S = Q K^T and O += P V as tcgen05.mma, accumulators in TMEM)
+//   warps 0-3: softmax of query tile 0 (thread = row: TMEM lane)
+//   warps 4-7: softmax of query tile 1
+// The two query tiles alternate on the tensor pipe: while the softmax warps of one tile
+// turn S into P, the MMAs of the other tile run.  P is written back over S in TMEM as
+// packed bf16 and is the A operand of the PV MMA; V is read MN-major straight from the
+// K/V layout, so nothing is transposed.  Running max / sum live in registers; O in TMEM
+// is rescaled only when the row max grows by more than 2^8, and the carried O of earlier
+// ring steps is folded in once, in the epilogue.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+#include <cstdio>
+#include <cstring>
+
 #include "host_util.h"
+#include "tc_common.cuh"
+
 namespace ra {
-const char* tc_fwd_unsupported_reason(const FwdParams&, int) { return "not built yet"; }
-cudaError_t tc_fwd_block(const FwdParams&, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kFwdThreads = 320;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
+
+struct FwdTcParams {
+  CUtensorMap map_q, map_k, map_v;
+  FwdParams p;
+  const TileMeta* meta_q;   // [b][n_q_tiles]  (NULL when there is no mask)
+  const TileMeta* meta_kv;  // [b][n_kv_tiles]
+  int n_q_tiles, n_kv_tiles;
+  unsigned int* status;
+};
+
+enum Bar {
+  Q_FULL0 = 0, Q_FULL1, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1,
+  S_FULL0, S_FULL1, P_FULL0, P_FULL1, O_FULL, NUM_BARS
+};
+
+template <int D>
+__global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_constant__ FwdTcParams P) {
+  constexpr int TILE_BYTES = kTileRows * D * 2;
+  constexpr int PANELS = D / 64;           // 64-element (128-byte) panels per row
+  constexpr int PANEL_BYTES = kTileRows * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + 2 * TILE_BYTES;
+  uint8_t* sV = sK + 2 * TILE_BYTES;
+  uint16_t* list = reinterpret_cast<uint16_t*>(sV + 2 * TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(list + kMaxTiles);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  int* count_slot = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const FwdParams& p = P.p;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh_count = p.b * p.h;
+  const int n_pairs = (P.n_q_tiles + 1) / 2;
+  const int bh = blockIdx.x % bh_count;
+  const int pair = n_pairs - 1 - blockIdx.x / bh_count;  // heaviest causal rows first
+  const int hh = bh % p.h, bb = bh / p.h;
+  const int qt0 = pair * 2;
+  const int ntile = (qt0 + 1 < P.n_q_tiles) ? 2 : 1;
+  const uint32_t kinds = p.mod.kinds;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_BARS; ++i) {
+      uint32_t cnt = (i == P_FULL0 || i == P_FULL1) ? 128u : 1u;
+      mbar_init(&bars[i], cnt);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0) {
+    // List of K/V tiles this CTA visits: index in bits 0-11, "query tile t needs mask
+    // arithmetic on it" in bit 12+t.  Tiles masked for both query tiles are left out.
+    int cnt = 0;
+    TileMeta mq0, mq1;
+    const bool masked = (kinds & kMaskKinds) != 0;
+    if (masked) {
+      mq0 = P.meta_q[bb * P.n_q_tiles + qt0];
+      mq1 = P.meta_q[bb * P.n_q_tiles + qt0 + (ntile - 1)];
+    }
+    for (int base = 0; base < P.n_kv_tiles; base += 32) {
+      const int j = base + lane;
+      uint32_t code = 0;
+      bool active = j < P.n_kv_tiles;
+      if (active && masked) {
+        const TileMeta mk = P.meta_kv[bb * P.n_kv_tiles + j];
+        const int c0 = classify_tiles(kinds, p.mod.window, mq0, mk);
+        const int c1 = ntile == 2 ? classify_tiles(kinds, p.mod.window, mq1, mk) : 0;
+        active = (c0 != 0) || (c1 != 0);
+        code = (c0 != 1 ? 1u : 0u) | (c1 != 1 ? 2u : 0u);
+      }
+      const uint32_t vote = __ballot_sync(0xffffffffu, active);
+      if (active) list[cnt + __popc(vote & ((1u << lane) - 1))] = (uint16_t)(j | (code << 12));
+      cnt += __popc(vote);
+    }
+    if (lane == 0) *count_slot = cnt;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int count = *count_slot;
+  const uint32_t tmem_S[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tmem_O[2] = {tmem_base + 256, tmem_base + 256 + D};
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&P.map_q);
+      prefetch_tensormap(&P.map_k);
+      prefetch_tensormap(&P.map_v);
+      for (int t = 0; t < ntile; ++t) {
+        mbar_arrive_expect_tx(&bars[Q_FULL0 + t], TILE_BYTES);
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_4d(sQ + t * TILE_BYTES + pn * PANEL_BYTES, &P.map_q, &bars[Q_FULL0 + t], pn * 64, hh,
+                      (qt0 + t) * kTileRows, bb);
+      }
+      for (int i = 0; i < count; ++i) {
+        const int j = list[i] & 0xFFF, s = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(&bars[K_EMPTY0 + s], ph ^ 1, abort_flag, P.status, kStFwdProducer)) break;
+        mbar_arrive_expect_tx(&bars[K_FULL0 + s], TILE_BYTES);
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_4d(sK + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_k, &bars[K_FULL0 + s], pn * 64, hh,
+                      j * kTileRows, bb);
+        if (!mbar_wait(&bars[V_EMPTY0 + s], ph ^ 1, abort_flag, P.status, kStFwdProducer)) break;
+        mbar_arrive_expect_tx(&bars[V_FULL0 + s], TILE_BYTES);
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_4d(sV + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_v, &bars[V_FULL0 + s], pn * 64, hh,
+                      j * kTileRows, bb);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && count > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool ok = true;
+      auto issue_s = [&](int t, int stage) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
+          mma_ss(tmem_S[t], make_smem_desc(q_addr + t * TILE_BYTES + off, 16, 1024),
+                 make_smem_desc(k_addr + stage * TILE_BYTES + off, 16, 1024), idesc_qk, kk > 0);
+        }
+        tc_commit(&bars[S_FULL0 + t]);
+      };
+      auto issue_pv = [&](int t, int stage, bool first_tile) {
+#pragma unroll
+        for (int kk = 0; kk < kTileRows / 16; ++kk)
+          mma_ts(tmem_O[t], tmem_S[t] + kk * 8,
+                 make_smem_desc(v_addr + stage * TILE_BYTES + kk * 2048, PANEL_BYTES, 1024), idesc_pv,
+                 (!first_tile) || kk > 0);
+      };
+      for (int t = 0; t < ntile && ok; ++t)
+        ok = mbar_wait(&bars[Q_FULL0 + t], 0, abort_flag, P.status, kStFwdMma);
+      if (ok) ok = mbar_wait(&bars[K_FULL0], 0, abort_flag, P.status, kStFwdMma);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < ntile; ++t) issue_s(t, 0);
+        tc_commit(&bars[K_EMPTY0]);
+      }
+      for (int i = 0; i < count && ok; ++i) {
+        const int s = i & 1, sn = (i + 1) & 1;
+        const uint32_t ph = (i >> 1) & 1, phn = ((i + 1) >> 1) & 1;
+        const bool has_next = i + 1 < count;
+        if (has_next && !(ok = mbar_wait(&bars[K_FULL0 + sn], phn, abort_flag, P.status, kStFwdMma))) break;
+        if (!(ok = mbar_wait(&bars[V_FULL0 + s], ph, abort_flag, P.status, kStFwdMma))) break;
+        for (int t = 0; t < ntile; ++t) {
+          if (!(ok = mbar_wait(&bars[P_FULL0 + t], i & 1, abort_flag, P.status, kStFwdMma))) break;
+          tc_fence_after();
+          issue_pv(t, s, i == 0);
+          if (t == ntile - 1) tc_commit(&bars[V_EMPTY0 + s]);
+          if (has_next) {
+            issue_s(t, sn);
+            if (t == ntile - 1) tc_commit(&bars[K_EMPTY0 + sn]);
+          }
+        }
+      }
+      if (ok) tc_commit(&bars[O_FULL]);
+    }
+  } else if (warp < 4 * ntile) {
+    // ------------------------------------------------------------ softmax + epilogue
+    const int t = warp >> 2;
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const int q_row = (qt0 + t) * kTileRows + row_in_tile;
+    const int64_t state_row = ((int64_t)bb * p.h + hh) * p.lq + q_row;
+    const float scale2 = p.scale * kLog2e;
+
+    float m_ref = -INFINITY, l_run = 0.f, alpha_total = 1.f;
+    if (!p.first) {
+      m_ref = p.m[state_row] * kLog2e;
+      l_run = p.l[state_row];
+    }
+    float m_true = m_ref;
+    int32_t qpos = 0, qseg = 0;
+    bool qpre = false;
+    if (p.mod.q_pos) qpos = p.mod.q_pos[(int64_t)bb * p.lq + q_row];
+    if (p.mod.q_seg) qseg = p.mod.q_seg[(int64_t)bb * p.lq + q_row];
+    if (p.mod.q_pre) qpre = p.mod.q_pre[(int64_t)bb * p.lq + q_row] != 0;
+    const bool alibi = (kinds & RA_MOD_ALIBI) != 0;
+    const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
+    bool ok = true;
+
+    for (int i = 0; i < count; ++i) {
+      const int j = list[i] & 0xFFF;
+      const bool need_mask = ((list[i] >> (12 + t)) & 1) != 0;
+      if (!(ok = mbar_wait(&bars[S_FULL0 + t], i & 1, abort_flag, P.status, kStFwdSoftmax))) break;
+      tc_fence_after();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[t] + lane_off + c * 32, r[c]);
+      tc_wait_ld();
+      float mx = -INFINITY;
+      if (need_mask || alibi) {
+        const int64_t kv0 = (int64_t)bb * p.lk + (int64_t)j * kTileRows;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e;
+            const int32_t kpos = p.mod.kv_pos ? __ldg(p.mod.kv_pos + kv0 + col) : 0;
+            const int32_t kseg = p.mod.kv_seg ? __ldg(p.mod.kv_seg + kv0 + col) : 0;
+            const bool kpre = p.mod.kv_pre ? (__ldg(p.mod.kv_pre + kv0 + col) != 0) : false;
+            float x = __uint_as_float(r[c][e]) * scale2;
+            x = apply_mod(x, need_mask ? kinds : (kinds & RA_MOD_ALIBI), p.mod.window, slope2, qpos, qseg, qpre,
+                          kpos, kseg, kpre);
+            r[c][e] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float x = __uint_as_float(r[c][e]) * scale2;
+            r[c][e] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+      }
+      const float m_new = fmaxf(m_true, mx);
+      m_true = m_new;
+      const bool need = (m_new > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - m_new);
+        m_ref = m_new;
+        l_run *= alpha;
+        alpha_total *= alpha;
+        if (i > 0) {  // O of this tile holds the sum over the tiles before this one
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_O[t] + lane_off + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(tmem_O[t] + lane_off + c * 32, o);
+          }
+        }
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = ex2(__uint_as_float(r[c][2 * e]) - m_use);
+          const float p1 = ex2(__uint_as_float(r[c][2 * e + 1]) - m_use);
+          sum += p0 + p1;
+          pk[e] = pack_bf16(p0, p1);
+        }
+        tmem_st16(tmem_S[t] + lane_off + c * 16, pk);
+      }
+      l_run += sum;
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[P_FULL0 + t]);
+    }
+
+    // Epilogue: fold in the carried state of earlier ring steps, bring (o, m, l) to the
+    // exact running max, store.
+    if (ok && count > 0) ok = mbar_wait(&bars[O_FULL], 0, abort_flag, P.status, kStFwdSoftmax);
+    if (ok) {
+      tc_fence_after();
+      const float beta = (m_ref == -INFINITY) ? 1.f : ex2(m_ref - m_true);
+      const float in_scale = p.first ? 0.f : alpha_total * beta;
+      float* o_row = p.o + state_row * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (count > 0) {
+          tmem_ld32(tmem_O[t] + lane_off + c * 32, o);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (!p.first) prev = *reinterpret_cast<const float4*>(o_row + c * 32 + e);
+          float4 out;
+          out.x = __uint_as_float(o[e]) * beta + prev.x * in_scale;
+          out.y = __uint_as_float(o[e + 1]) * beta + prev.y * in_scale;
+          out.z = __uint_as_float(o[e + 2]) * beta + prev.z * in_scale;
+          out.w = __uint_as_float(o[e + 3]) * beta + prev.w * in_scale;
+          *reinterpret_cast<float4*>(o_row + c * 32 + e) = out;
+        }
+      }
+      p.m[state_row] = m_true * (1.f / kLog2e);
+      p.l[state_row] = l_run * beta;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
 }
+
+// -----------------------------------------------------------------------------------------
+__global__ void tile_meta_kernel(TileMeta* __restrict__ out, const int32_t* __restrict__ pos,
+                                 const int32_t* __restrict__ seg, const uint8_t* __restrict__ pre, int len) {
+  // one warp per tile: 4 tokens per lane
+  const int n_tiles = len / kTileRows;
+  const int tile = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, bb = blockIdx.y;
+  if (tile >= n_tiles) return;
+  const int64_t base = (int64_t)bb * len + (int64_t)tile * kTileRows;
+  int pmin = INT32_MAX, pmax = INT32_MIN, smin = INT32_MAX, smax = INT32_MIN, any = 0, all = 1;
+  for (int e = lane; e < kTileRows; e += 32) {
+    if (pos) {
+      int v = pos[base + e];
+      pmin = min(pmin, v);
+      pmax = max(pmax, v);
+    }
+    if (seg) {
+      int v = seg[base + e];
+      smin = min(smin, v);
+      smax = max(smax, v);
+    }
+    if (pre) {
+      int v = pre[base + e] != 0;
+      any |= v;
+      all &= v;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    pmin = min(pmin, __shfl_xor_sync(0xffffffffu, pmin, o));
+    pmax = max(pmax, __shfl_xor_sync(0xffffffffu, pmax, o));
+    smin = min(smin, __shfl_xor_sync(0xffffffffu, smin, o));
+    smax = max(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+    any |= __shfl_xor_sync(0xffffffffu, any, o);
+    all &= __shfl_xor_sync(0xffffffffu, all, o);
+  }
+  if (lane == 0) {
+    TileMeta m;
+    m.pos_min = pos ? pmin : 0;
+    m.pos_max = pos ? pmax : 0;
+    m.seg_min = seg ? smin : 0;
+    m.seg_max = seg ? smax : 0;
+    m.pre_any = pre ? any : 0;
+    m.pre_all = pre ? all : 0;
+    m.pad0 = m.pad1 = 0;
+    out[(int64_t)bb * n_tiles + tile] = m;
+  }
+}
+
+__device__ unsigned int g_status_word = 0;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+template <int D>
+cudaError_t launch_fwd(const FwdTcParams& P, cudaStream_t s) {
+  constexpr size_t kSmem = 6 * kTileRows * D * 2 + kMaxTiles * 2 + NUM_BARS * 8 + 64 + 1024;
+  constexpr size_t kRequest = kSmem < 120 * 1024 ? 120 * 1024 : kSmem;  // one CTA per SM: it owns all of TMEM
+  auto kern = tc_fwd_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRequest);
+  if (e != cudaSuccess) return e;
+  const int n_pairs = (P.n_q_tiles + 1) / 2;
+  kern<<<n_pairs * P.p.b * P.p.h, kFwdThreads, kRequest, s>>>(P);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+unsigned int* device_status_word() {
+  unsigned int* ptr = nullptr;
+  if (cudaGetSymbolAddress((void**)&ptr, g_status_word) != cudaSuccess) return nullptr;
+  return ptr;
+}
+
+bool make_tile_map(CUtensorMap* map, const TensorView& t, int b, int len, int h, int d, int box_rows,
+                   const char** why) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    *why = "cuTensorMapEncodeTiled is not available from this driver";
+    return false;
+  }
+  const cuuint64_t row_bytes = (cuuint64_t)d * 2;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)h, (cuuint64_t)len, (cuuint64_t)b};
+  cuuint64_t strides[3] = {h > 1 ? (cuuint64_t)t.sh * 2 : row_bytes, len > 1 ? (cuuint64_t)t.sl * 2 : row_bytes,
+                           b > 1 ? (cuuint64_t)t.sb * 2 : row_bytes};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(t.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *why = "the driver refused the tensor map for these strides";
+    return false;
+  }
+  return true;
+}
+
+cudaError_t launch_tile_meta(TileMeta* out, const int32_t* pos, const int32_t* seg, const uint8_t* pre, int b,
+                             int len, cudaStream_t s) {
+  const int n_tiles = len / kTileRows;
+  dim3 grid((n_tiles + 7) / 8, b);
+  tile_meta_kernel<<<grid, 256, 0, s>>>(out, pos, seg, pre, len);
+  count_launch();
+  return cudaGetLastError();
+}
+
+static bool aligned16(const TensorView& t) {
+  return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && (t.sb % 8) == 0 && (t.sl % 8) == 0 && (t.sh % 8) == 0;
+}
+
+const char* tc_fwd_unsupported_reason(const FwdParams& p, int dtype) {
+  if (dtype != RA_DTYPE_BF16) return "inputs are not bf16";
+  if (p.dk != p.dv || (p.dk != 64 && p.dk != 128)) return "head dims must be equal and 64 or 128";
+  if (p.lq % kTileRows || p.lk % kTileRows) return "lq and lk must be multiples of 128";
+  if (p.lq / kTileRows > kMaxTiles || p.lk / kTileRows > kMaxTiles) return "more than 4096 tiles along one axis";
+  if (p.mod.kinds & RA_MOD_DENSE) return "a dense bias tile is served by the CUDA-core kernels";
+  if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v)) return "q/k/v need 16-byte aligned base and strides";
+  return nullptr;
+}
+
+cudaError_t tc_fwd_block(const FwdParams& p, cudaStream_t s) {
+  FwdTcParams P;
+  memset(&P, 0, sizeof(P));
+  P.p = p;
+  P.n_q_tiles = p.lq / kTileRows;
+  P.n_kv_tiles = p.lk / kTileRows;
+  const char* why = nullptr;
+  if (!make_tile_map(&P.map_q, p.q, p.b, p.lq, p.h, p.dk, kTileRows, &why) ||
+      !make_tile_map(&P.map_k, p.k, p.b, p.lk, p.h, p.dk, kTileRows, &why) ||
+      !make_tile_map(&P.map_v, p.v, p.b, p.lk, p.h, p.dv, kTileRows, &why))
+    return cudaErrorNotSupported;
+  P.status = device_status_word();
+  if (!P.status) return cudaErrorInvalidSymbol;
+  TileMeta* meta = nullptr;
+  cudaError_t e;
+  if (p.mod.kinds & kMaskKinds) {
+    const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
+    if ((e = cudaMallocAsync((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
+    TileMeta* mq = meta;
+    TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
+    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess) return e;
+    if ((e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s)) != cudaSuccess) return e;
+    P.meta_q = mq;
+    P.meta_kv = mk;
+  }
+  e = p.dk == 128 ? launch_fwd<128>(P, s) : launch_fwd<64>(P, s);
+  if (meta) cudaFreeAsync(meta, s);
+  return e;
+}
+
+}  // namespace ra

@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "host_util.h"
+#include "tc_common.cuh"
 
 namespace ra {
 
@@ -92,11 +93,14 @@ int run_fwd_block(const FwdParams& p, int dtype, cudaStream_t s) {
     const char* why = tc_fwd_unsupported_reason(p, dtype);
     if (!why) {
       cudaError_t e = tc_fwd_block(p, s);
-      if (e != cudaSuccess) return fail_cuda(e, "tcgen05 forward block");
-      g_last_impl = RA_IMPL_TCGEN05;
-      return 0;
+      if (e == cudaSuccess) {
+        g_last_impl = RA_IMPL_TCGEN05;
+        return 0;
+      }
+      // cudaErrorNotSupported: the driver refused a tensor map for these strides
+      if (e != cudaErrorNotSupported || impl == RA_IMPL_TCGEN05) return fail_cuda(e, "tcgen05 forward block");
     }
-    if (impl == RA_IMPL_TCGEN05) return fail(-20, "tcgen05 forward does not take this call: %s", why);
+    if (why && impl == RA_IMPL_TCGEN05) return fail(-20, "tcgen05 forward does not take this call: %s", why);
   }
   cudaError_t e = simt_fwd_block(p, dtype, s);
   if (e != cudaSuccess) return fail_cuda(e, "simt forward block");
@@ -110,11 +114,13 @@ int run_bwd_block(const BwdParams& p, int dtype, cudaStream_t s) {
     const char* why = tc_bwd_unsupported_reason(p, dtype);
     if (!why) {
       cudaError_t e = tc_bwd_block(p, s);
-      if (e != cudaSuccess) return fail_cuda(e, "tcgen05 backward block");
-      g_last_impl = RA_IMPL_TCGEN05;
-      return 0;
+      if (e == cudaSuccess) {
+        g_last_impl = RA_IMPL_TCGEN05;
+        return 0;
+      }
+      if (e != cudaErrorNotSupported || impl == RA_IMPL_TCGEN05) return fail_cuda(e, "tcgen05 backward block");
     }
-    if (impl == RA_IMPL_TCGEN05) return fail(-20, "tcgen05 backward does not take this call: %s", why);
+    if (why && impl == RA_IMPL_TCGEN05) return fail(-20, "tcgen05 backward does not take this call: %s", why);
   }
   cudaError_t e = simt_bwd_block(p, dtype, s);
   if (e != cudaSuccess) return fail_cuda(e, "simt backward block");
@@ -137,6 +143,20 @@ int ra_set_impl(int impl) {
 }
 int ra_last_impl(void) { return g_last_impl; }
 int64_t ra_launch_count(void) { return g_launches.load(); }
+
+int ra_device_status(uint32_t* bits) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
+  unsigned int* word = device_status_word();
+  if (!word) return fail(RA_ERR_CUDA, "status word symbol not found");
+  unsigned int v = 0, zero = 0;
+  if ((e = cudaMemcpy(&v, word, sizeof(v), cudaMemcpyDeviceToHost)) != cudaSuccess) return fail_cuda(e, "cudaMemcpy");
+  if (v && (e = cudaMemcpy(word, &zero, sizeof(zero), cudaMemcpyHostToDevice)) != cudaSuccess)
+    return fail_cuda(e, "cudaMemcpy");
+  if (bits) *bits = v;
+  if (v) return fail(RA_ERR_DEVICE_STATUS, "a bounded wait ran out inside a kernel (status bits 0x%x)", v);
+  return 0;
+}
 
 int ra_fwd_block(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_t* k,
                  const ra_tensor_t* v, const ra_score_mod_t* mod, float* o, float* m, float* l,

@@ -314,8 +314,9 @@ __global__ void __launch_bounds__(NT) simt_bwd_kernel(const BwdParams p) {
           // ring.py:146.  With a dense bias tile a row that saw no key (L = -inf) gives
           // exp(-inf + inf) = NaN exactly like the reference; the compiled-in masks
           // define p = 0 on a masked pair, so such rows contribute nothing.
-          pe = (s[i][j] == -INFINITY && !(p.mod.kinds & RA_MOD_DENSE)) ? 0.f : expf(s[i][j] - L);
-          ds = pe * (dp[i][j] - dl) * p.scale;     // ring.py:152
+          const bool masked = (s[i][j] == -INFINITY) && !(p.mod.kinds & RA_MOD_DENSE);
+          pe = masked ? 0.f : expf(s[i][j] - L);
+          ds = masked ? 0.f : pe * (dp[i][j] - dl) * p.scale;  // ring.py:152 (delta is NaN on such rows)
         }
         Ps[(ty * 4 + i) * LDP + tx + 16 * j] = pe;
         Ds[(ty * 4 + i) * LDP + tx + 16 * j] = ds;

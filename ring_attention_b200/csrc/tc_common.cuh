@@ -1,0 +1,64 @@
+// Pieces shared by the tcgen05 forward and backward block kernels: per-tile mask
+// metadata, tile classification, TMA descriptor construction, the device status word.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace ra {
+
+constexpr int kTileRows = 128;     // rows of one q tile / one kv tile
+constexpr int kMaxTiles = 4096;    // most tiles one block (shard) may have along either axis
+
+// Range summary of the per-token score-mod arrays over one 128-token tile.
+struct TileMeta {
+  int32_t pos_min, pos_max, seg_min, seg_max;
+  int32_t pre_any, pre_all, pad0, pad1;
+};
+
+// 0: every pair of the tile pair is masked; 1: every pair is visible; 2: mixed.
+__device__ __forceinline__ int classify_tiles(uint32_t kinds, int32_t window, const TileMeta& q,
+                                              const TileMeta& k) {
+  bool skip = false, full = true;
+  if (kinds & RA_MOD_SEGMENT) {
+    if (q.seg_max < k.seg_min || k.seg_max < q.seg_min) skip = true;
+    if (!(q.seg_min == q.seg_max && k.seg_min == k.seg_max && q.seg_min == k.seg_min)) full = false;
+  }
+  const bool causal_none = k.pos_min > q.pos_max, causal_all = k.pos_max <= q.pos_min;
+  if (kinds & RA_MOD_CAUSAL) {
+    if (causal_none) skip = true;
+    if (!causal_all) full = false;
+  } else if (kinds & RA_MOD_PREFIX) {
+    const bool pre_none = !(q.pre_any && k.pre_any), pre_all = q.pre_all && k.pre_all;
+    if (causal_none && pre_none) skip = true;
+    if (!(causal_all || pre_all)) full = false;
+  }
+  if (kinds & RA_MOD_WINDOW) {
+    if ((long long)q.pos_min - (long long)k.pos_max >= (long long)window) skip = true;
+    if (!((long long)q.pos_max - (long long)k.pos_min < (long long)window)) full = false;
+  }
+  return skip ? 0 : (full ? 1 : 2);
+}
+
+constexpr uint32_t kMaskKinds = RA_MOD_CAUSAL | RA_MOD_SEGMENT | RA_MOD_PREFIX | RA_MOD_WINDOW;
+
+// Host side -----------------------------------------------------------------------------
+// Tensor map over a [b, len, h, d] bf16 tensor with box {64 elements of d, 1 head, 128 rows,
+// 1 batch} and the 128-byte swizzle the UMMA descriptors expect.  Returns false (with a
+// reason) when the driver refuses the layout.
+bool make_tile_map(CUtensorMap* map, const TensorView& t, int b, int len, int h, int d, int box_rows,
+                   const char** why);
+
+// Launches the kernel that fills TileMeta[b][n_tiles] for one side (q or kv).
+cudaError_t launch_tile_meta(TileMeta* out, const int32_t* pos, const int32_t* seg, const uint8_t* pre,
+                             int b, int len, cudaStream_t s);
+
+// Device status word of the current device (bit set = a bounded wait ran out).
+unsigned int* device_status_word();
+
+// Failure codes OR-ed into the status word.
+constexpr uint32_t kStFwdProducer = 1u << 0, kStFwdMma = 1u << 1, kStFwdSoftmax = 1u << 2;
+constexpr uint32_t kStBwdProducer = 1u << 8, kStBwdMma = 1u << 9, kStBwdCompute = 1u << 10;
+
+}  // namespace ra
