@@ -1,7 +1,437 @@
-// placeholder until the tcgen05 backward lands
-#include "common.cuh"
+// tcgen05 backward block kernel for sm_100a: adds one (Q block, K/V block) pair's
+// contribution to dQ, dK, dV; bf16 inputs, head dim 64 or 128.  It computes what
+// bwd_block / _bwd_kernel of the reference compute (ring_attention/ring_kernel.py:202-384,
+// math of ring.py:140-157), with delta = rowsum(dO * O) precomputed once per backward
+// instead of once per ring step (ring_kernel.py:227).
+//
+// One CTA owns a 128-row K/V tile (dK, dV accumulate in TMEM for the whole kernel) and
+// walks the 128-row query tiles.  Everything is computed transposed, so that the thread
+// that owns TMEM lane r owns key row r:
+//   S^T  = K Q^T          (SS MMA, both operands K-major)            -> TMEM [0,128)
+//   dP^T = V dO^T         (SS MMA)                                   -> TMEM [128,256)
+//   P^T  = exp2(S^T * c - L)          written back over S^T as packed bf16 (TMEM)
+//   dS^T = P^T * (dP^T - delta)       written to shared memory as bf16 (128B swizzle)
+//   dV  += P^T dO         (TS MMA: A from TMEM, B = dO read MN-major) -> TMEM [256,256+D)
+//   dK  += dS^T Q         (SS MMA: B = Q read MN-major)               -> TMEM [256+D,256+2D)
+//   dQ   = dS K           (SS MMA: A = dS^T tile read MN-major, B = K read MN-major)
+//                          -> TMEM [128,128+D), over dP^T, then added to global dQ with
+//                             vector float reductions.
+// warps 0-7: compute (two warpgroups split the 128 query columns), warp 8: TMA producer,
+// warp 9: MMA issuer.
+#include <cstring>
+
 #include "host_util.h"
+#include "tc_common.cuh"
+
 namespace ra {
-const char* tc_bwd_unsupported_reason(const BwdParams&, int) { return "not built yet"; }
-cudaError_t tc_bwd_block(const BwdParams&, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBwdThreads = 320;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdTcParams {
+  CUtensorMap map_q, map_k, map_v, map_do;
+  BwdParams p;
+  const TileMeta* meta_q;
+  const TileMeta* meta_kv;
+  int n_q_tiles, n_kv_tiles;
+  unsigned int* status;
+};
+
+enum Bar {
+  KV_FULL = 0, QDO_FULL0, QDO_FULL1, QDO_EMPTY0, QDO_EMPTY1, S_FULL, DP_FULL, P_READY, DS_READY, DS_FREE,
+  DQ_FULL, DQ_DRAINED, DKDV_FULL, NUM_BARS
+};
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
 }
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_constant__ BwdTcParams P) {
+  constexpr int TILE_BYTES = kTileRows * D * 2;
+  constexpr int PANELS = D / 64;
+  constexpr int PANEL_BYTES = kTileRows * 128;
+  constexpr int DS_BYTES = kTileRows * kTileRows * 2;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;          // 2 stages
+  uint8_t* sdO = sQ + 2 * TILE_BYTES;     // 2 stages
+  uint8_t* sdS = sdO + 2 * TILE_BYTES;    // [128 key rows][128 query cols] bf16, 2 panels, 128B swizzle
+  float* sL = reinterpret_cast<float*>(sdS + DS_BYTES);  // [2][128]
+  float* sDelta = sL + 2 * kTileRows;                     // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * kTileRows);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const BwdParams& p = P.p;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh_count = p.b * p.h;
+  const int bh = blockIdx.x % bh_count;
+  const int kt = blockIdx.x / bh_count;  // K/V tile; tile 0 has the most visible queries under a causal mask
+  const int hh = bh % p.h, bb = bh / p.h;
+  const uint32_t kinds = p.mod.kinds;
+  const bool masked = (kinds & kMaskKinds) != 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_BARS; ++i) {
+      uint32_t cnt = (i == P_READY || i == DS_READY || i == DQ_DRAINED) ? 256u : 1u;
+      mbar_init(&bars[i], cnt);
+    }
+    *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
+    if (*abort_flag) atomicOr(P.status, kStBwdProducer);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
+                 tmem_dK = tmem_base + 256 + D;
+  const bool bad = *abort_flag != 0;
+
+  TileMeta mk;
+  if (masked) mk = P.meta_kv[bb * P.n_kv_tiles + kt];
+  // Class of query tile i against this CTA's K/V tile: 0 skip, 1 all visible, 2 mixed.
+  auto tile_class = [&](int i) -> int {
+    if (!masked) return 1;
+    const TileMeta mq = P.meta_q[bb * P.n_q_tiles + i];
+    return classify_tiles(kinds, p.mod.window, mq, mk);
+  };
+  auto next_active = [&](int i) -> int {
+    while (i < P.n_q_tiles && tile_class(i) == 0) ++i;
+    return i;
+  };
+
+  if (bad) {
+    // fall through to the common exit
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&P.map_q);
+      prefetch_tensormap(&P.map_k);
+      prefetch_tensormap(&P.map_v);
+      prefetch_tensormap(&P.map_do);
+      int i = next_active(0);
+      if (i < P.n_q_tiles) {
+        mbar_arrive_expect_tx(&bars[KV_FULL], 2 * TILE_BYTES);
+        for (int pn = 0; pn < PANELS; ++pn) {
+          tma_load_4d(sK + pn * PANEL_BYTES, &P.map_k, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
+          tma_load_4d(sV + pn * PANEL_BYTES, &P.map_v, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
+        }
+      }
+      const int64_t row_base = ((int64_t)bb * p.h + hh) * p.lq;
+      for (int n = 0; i < P.n_q_tiles; i = next_active(i + 1), ++n) {
+        const int s = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        if (!mbar_wait(&bars[QDO_EMPTY0 + s], ph ^ 1, abort_flag, P.status, kStBwdProducer)) break;
+        mbar_arrive_expect_tx(&bars[QDO_FULL0 + s], 2 * TILE_BYTES + 2 * kTileRows * 4);
+        for (int pn = 0; pn < PANELS; ++pn) {
+          tma_load_4d(sQ + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_q, &bars[QDO_FULL0 + s], pn * 64, hh,
+                      i * kTileRows, bb);
+          tma_load_4d(sdO + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_do, &bars[QDO_FULL0 + s], pn * 64, hh,
+                      i * kTileRows, bb);
+        }
+        bulk_load(sL + s * kTileRows, p.lse + row_base + (int64_t)i * kTileRows, kTileRows * 4, &bars[QDO_FULL0 + s]);
+        bulk_load(sDelta + s * kTileRows, p.delta + row_base + (int64_t)i * kTileRows, kTileRows * 4,
+                  &bars[QDO_FULL0 + s]);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S^T, dP^T
+      constexpr uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);     // dV, dK: B MN-major
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);      // dQ: A and B MN-major
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sdO),
+                     ds_addr = smem_u32(sdS);
+      auto kmajor = [](uint32_t base, int kk) {
+        return make_smem_desc(base + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32, 16, 1024);
+      };
+      auto mnmajor = [](uint32_t base, int kk) { return make_smem_desc(base + kk * 2048, PANEL_BYTES, 1024); };
+      auto issue_s = [&](int stage) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem_S, kmajor(k_addr, kk), kmajor(q_addr + stage * TILE_BYTES, kk), idesc_s, kk > 0);
+        tc_commit(&bars[S_FULL]);
+      };
+      auto issue_dp = [&](int stage) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem_dP, kmajor(v_addr, kk), kmajor(do_addr + stage * TILE_BYTES, kk), idesc_s, kk > 0);
+        tc_commit(&bars[DP_FULL]);
+      };
+      bool ok = true;
+      int i = next_active(0);
+      if (i < P.n_q_tiles) {
+        ok = mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
+             mbar_wait(&bars[QDO_FULL0], 0, abort_flag, P.status, kStBwdMma);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+          issue_dp(0);
+        }
+        for (int n = 0; ok && i < P.n_q_tiles; ++n) {
+          const int s = n & 1, sn = (n + 1) & 1;
+          const uint32_t par = n & 1;
+          const int inext = next_active(i + 1);
+          // dV += P^T dO
+          if (!(ok = mbar_wait(&bars[P_READY], par, abort_flag, P.status, kStBwdMma))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t pcol = kk < 4 ? kk * 8 : 64 + (kk - 4) * 8;  // P^T columns of the two warpgroups
+            mma_ts(tmem_dV, tmem_S + pcol, mnmajor(do_addr + s * TILE_BYTES, kk), idesc_dv, (n > 0) || kk > 0);
+          }
+          // dQ = dS K (into the dP^T columns), dK += dS^T Q
+          if (!(ok = mbar_wait(&bars[DS_READY], par, abort_flag, P.status, kStBwdMma))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ss(tmem_dP, mnmajor(ds_addr, kk), mnmajor(k_addr, kk), idesc_dq, kk > 0);
+          tc_commit(&bars[DQ_FULL]);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ss(tmem_dK, kmajor(ds_addr, kk), mnmajor(q_addr + s * TILE_BYTES, kk), idesc_dv, (n > 0) || kk > 0);
+          tc_commit(&bars[QDO_EMPTY0 + s]);
+          tc_commit(&bars[DS_FREE]);
+          if (inext < P.n_q_tiles) {
+            if (!(ok = mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma))) break;
+            tc_fence_after();
+            issue_s(sn);
+            if (!(ok = mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma))) break;
+            tc_fence_after();
+            issue_dp(sn);
+          }
+          i = inext;
+        }
+        if (ok) tc_commit(&bars[DKDV_FULL]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ compute (warps 0-7)
+    const int g = warp >> 2;                         // warpgroup: query columns [64g, 64g+64)
+    const int r = (warp & 3) * 32 + lane;            // key row of this thread = TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const int kv_row = kt * kTileRows + r;
+    const float scale2 = p.scale * kLog2e;
+    const bool alibi = (kinds & RA_MOD_ALIBI) != 0;
+    const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
+    int32_t kpos = 0, kseg = 0;
+    bool kpre = false;
+    if (p.mod.kv_pos) kpos = p.mod.kv_pos[(int64_t)bb * p.lk + kv_row];
+    if (p.mod.kv_seg) kseg = p.mod.kv_seg[(int64_t)bb * p.lk + kv_row];
+    if (p.mod.kv_pre) kpre = p.mod.kv_pre[(int64_t)bb * p.lk + kv_row] != 0;
+    const int64_t qrow_base = ((int64_t)bb * p.h + hh) * p.lq;
+    bool ok = true;
+    int n = 0;
+    for (int i = next_active(0); i < P.n_q_tiles; i = next_active(i + 1), ++n) {
+      const int s = n & 1;
+      const uint32_t par = n & 1;
+      const bool need_mask = masked && tile_class(i) == 2;
+      if (!(ok = mbar_wait(&bars[QDO_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute))) break;
+      const float* Ls = sL + s * kTileRows + g * 64;
+      const float* Dls = sDelta + s * kTileRows + g * 64;
+      // ---- P^T = exp2(S^T * scale2 - L * log2e) on this warpgroup's 64 query columns
+      if (!(ok = mbar_wait(&bars[S_FULL], par, abort_flag, P.status, kStBwdCompute))) break;
+      tc_fence_after();
+      uint32_t sv[2][32];
+      tmem_ld32(tmem_S + lane_off + g * 64, sv[0]);
+      tmem_ld32(tmem_S + lane_off + g * 64 + 32, sv[1]);
+      tc_wait_ld();
+      float pf[64];
+      const int64_t q0 = (int64_t)bb * p.lq + (int64_t)i * kTileRows + g * 64;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float x = __uint_as_float(sv[c >> 5][c & 31]) * scale2;
+        if (need_mask || alibi) {
+          const int32_t qpos = p.mod.q_pos ? __ldg(p.mod.q_pos + q0 + c) : 0;
+          const int32_t qseg = p.mod.q_seg ? __ldg(p.mod.q_seg + q0 + c) : 0;
+          const bool qpre = p.mod.q_pre ? (__ldg(p.mod.q_pre + q0 + c) != 0) : false;
+          x = apply_mod(x, need_mask ? kinds : (kinds & RA_MOD_ALIBI), p.mod.window, slope2, qpos, qseg, qpre, kpos,
+                        kseg, kpre);
+        }
+        // a masked pair contributes nothing, also on a row whose L is -inf
+        pf[c] = (x == -INFINITY) ? 0.f : ex2(x - Ls[c] * kLog2e);
+      }
+      {
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) pk[e] = pack_bf16(pf[2 * e], pf[2 * e + 1]);
+        tmem_st32(tmem_S + lane_off + g * 64, pk);  // P^T of warpgroup g: 32 packed columns at S column 64g
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[P_READY]);
+      // ---- dS^T = P^T * (dP^T - delta)
+      if (!(ok = mbar_wait(&bars[DP_FULL], par, abort_flag, P.status, kStBwdCompute))) break;
+      tc_fence_after();
+      tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
+      tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
+      tc_wait_ld();
+      if (!(ok = mbar_wait(&bars[DS_FREE], par ^ 1, abort_flag, P.status, kStBwdCompute))) break;
+      {
+        uint8_t* row_ptr = sdS + g * PANEL_BYTES + r * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = ch * 8 + e * 2;
+            const float d0 = pf[c] * (__uint_as_float(sv[c >> 5][c & 31]) - Dls[c]);
+            const float d1 = pf[c + 1] * (__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - Dls[c + 1]);
+            w[e] = pack_bf16(d0, d1);
+          }
+          *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars[DS_READY]);
+      // ---- dQ tile: rows are queries now; add this warpgroup's half of the columns
+      if (!(ok = mbar_wait(&bars[DQ_FULL], par, abort_flag, P.status, kStBwdCompute))) break;
+      tc_fence_after();
+      {
+        constexpr int HALF = D / 2;
+        float* dq_row = p.dq + (qrow_base + (int64_t)i * kTileRows + r) * D + g * HALF;
+#pragma unroll
+        for (int c = 0; c < HALF / 32; ++c) {
+          tmem_ld32(tmem_dP + lane_off + g * HALF + c * 32, sv[0]);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4(dq_row + c * 32 + e, __uint_as_float(sv[0][e]) * p.scale, __uint_as_float(sv[0][e + 1]) * p.scale,
+                       __uint_as_float(sv[0][e + 2]) * p.scale, __uint_as_float(sv[0][e + 3]) * p.scale);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars[DQ_DRAINED]);
+    }
+    // ---- epilogue: dK, dV of this K/V tile
+    if (ok && n > 0) ok = mbar_wait(&bars[DKDV_FULL], 0, abort_flag, P.status, kStBwdCompute);
+    if (ok && n > 0) {
+      tc_fence_after();
+      constexpr int HALF = D / 2;
+      const int64_t krow = ((int64_t)bb * p.h + hh) * p.lk + kv_row;
+      float* dk_row = p.dk + krow * D + g * HALF;
+      float* dv_row = p.dv + krow * D + g * HALF;
+      uint32_t a[32];
+#pragma unroll
+      for (int c = 0; c < HALF / 32; ++c) {
+        tmem_ld32(tmem_dK + lane_off + g * HALF + c * 32, a);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 cur = *reinterpret_cast<float4*>(dk_row + c * 32 + e);
+          cur.x += __uint_as_float(a[e]) * p.scale;
+          cur.y += __uint_as_float(a[e + 1]) * p.scale;
+          cur.z += __uint_as_float(a[e + 2]) * p.scale;
+          cur.w += __uint_as_float(a[e + 3]) * p.scale;
+          *reinterpret_cast<float4*>(dk_row + c * 32 + e) = cur;
+        }
+        tmem_ld32(tmem_dV + lane_off + g * HALF + c * 32, a);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 cur = *reinterpret_cast<float4*>(dv_row + c * 32 + e);
+          cur.x += __uint_as_float(a[e]);
+          cur.y += __uint_as_float(a[e + 1]);
+          cur.z += __uint_as_float(a[e + 2]);
+          cur.w += __uint_as_float(a[e + 3]);
+          *reinterpret_cast<float4*>(dv_row + c * 32 + e) = cur;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+cudaError_t launch_bwd(const BwdTcParams& P, cudaStream_t s) {
+  constexpr size_t kSmem = 6 * kTileRows * D * 2 + kTileRows * kTileRows * 2 + 4 * kTileRows * 4 + NUM_BARS * 8 + 64;
+  constexpr size_t kRequest = kSmem < 120 * 1024 ? 120 * 1024 : kSmem;  // one CTA per SM: it owns all of TMEM
+  auto kern = tc_bwd_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRequest);
+  if (e != cudaSuccess) return e;
+  kern<<<P.n_kv_tiles * P.p.b * P.p.h, kBwdThreads, kRequest, s>>>(P);
+  count_launch();
+  return cudaGetLastError();
+}
+
+bool aligned16(const TensorView& t) {
+  return (reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0 && (t.sb % 8) == 0 && (t.sl % 8) == 0 && (t.sh % 8) == 0;
+}
+
+}  // namespace
+
+const char* tc_bwd_unsupported_reason(const BwdParams& p, int dtype) {
+  if (dtype != RA_DTYPE_BF16) return "inputs are not bf16";
+  if (p.dk_dim != p.dv_dim || (p.dk_dim != 64 && p.dk_dim != 128)) return "head dims must be equal and 64 or 128";
+  if (p.lq % kTileRows || p.lk % kTileRows) return "lq and lk must be multiples of 128";
+  if (p.lq / kTileRows > kMaxTiles || p.lk / kTileRows > kMaxTiles) return "more than 4096 tiles along one axis";
+  if (p.mod.kinds & RA_MOD_DENSE) return "a dense bias tile is served by the CUDA-core kernels";
+  if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.dout))
+    return "q/k/v/dout need 16-byte aligned base and strides";
+  if ((reinterpret_cast<uintptr_t>(p.lse) & 15) || (reinterpret_cast<uintptr_t>(p.delta) & 15) ||
+      (reinterpret_cast<uintptr_t>(p.dq) & 15) || (reinterpret_cast<uintptr_t>(p.dk) & 15) ||
+      (reinterpret_cast<uintptr_t>(p.dv) & 15))
+    return "lse/delta/dq/dk/dv need 16-byte aligned bases";
+  return nullptr;
+}
+
+cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
+  BwdTcParams P;
+  memset(&P, 0, sizeof(P));
+  P.p = p;
+  P.n_q_tiles = p.lq / kTileRows;
+  P.n_kv_tiles = p.lk / kTileRows;
+  const char* why = nullptr;
+  if (!make_tile_map(&P.map_q, p.q, p.b, p.lq, p.h, p.dk_dim, kTileRows, &why) ||
+      !make_tile_map(&P.map_k, p.k, p.b, p.lk, p.h, p.dk_dim, kTileRows, &why) ||
+      !make_tile_map(&P.map_v, p.v, p.b, p.lk, p.h, p.dv_dim, kTileRows, &why) ||
+      !make_tile_map(&P.map_do, p.dout, p.b, p.lq, p.h, p.dv_dim, kTileRows, &why))
+    return cudaErrorNotSupported;
+  P.status = device_status_word();
+  if (!P.status) return cudaErrorInvalidSymbol;
+  TileMeta* meta = nullptr;
+  cudaError_t e;
+  if (p.mod.kinds & kMaskKinds) {
+    const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
+    if ((e = cudaMallocAsync((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
+    TileMeta* mq = meta;
+    TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
+    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess) return e;
+    if ((e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s)) != cudaSuccess) return e;
+    P.meta_q = mq;
+    P.meta_kv = mk;
+  }
+  e = p.dk_dim == 128 ? launch_bwd<128>(P, s) : launch_bwd<64>(P, s);
+  if (meta) cudaFreeAsync(meta, s);
+  return e;
+}
+
+}  // namespace ra
