@@ -197,9 +197,10 @@ def test_score_mod_variants_match_dense_bias(mod, dtype):
                                                                  bias_kv_kwargs=kkw, block_impl="simt"), tq, tk, tv, tdo)
     check_close(out, O.mha(q, k, v, bias), dtype, "out")
     rq, rk, rv = O.mha_grads(q, k, v, do, bias)
-    check_close(dq, rq, dtype, "dq", 2e-5)
-    check_close(dk, rk, dtype, "dk", 2e-5)
-    check_close(dv, rv, dtype, "dv", 2e-5)
+    # shuffled positions leave some rows without any visible key: see check_close
+    check_close(dq, rq, dtype, "dq", 2e-5, nan="finite")
+    check_close(dk, rk, dtype, "dk", 2e-5, nan="finite")
+    check_close(dv, rv, dtype, "dv", 2e-5, nan="finite")
 
 
 @pytest.mark.parametrize("name", list(G.CASES))
