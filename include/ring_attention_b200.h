@@ -114,6 +114,30 @@ int ra_fwd_block(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_
                  const ra_tensor_t* v, const ra_score_mod_t* mod, float* o, float* m, float* l,
                  int first, void* stream);
 
+/* ra_fwd_block_static: the tensor-core forward block for hosts that must not allocate.
+ * It has no counterpart in the reference.  ra_fwd_block takes a few kilobytes of device
+ * scratch per call from the stream-ordered allocator (the per-tile mask summaries).  A
+ * caller that runs inside an XLA / JAX FFI custom call, where XLA's allocator already owns
+ * nearly all device memory, or a server that has given all free memory to its own arena,
+ * cannot rely on that succeeding.  This entry point does the same work with the scratch
+ * in a fixed 512 KiB array inside the library (held by every GPU that loads the library,
+ * until the process ends) and calls no allocating routine.
+ *   - Arguments and results are those of ra_fwd_block; the caller still owns q, k, v, the
+ *     score-mod arrays and the carried state (o, m, l).
+ *   - It serves only calls the tcgen05 forward takes (bf16, head dim 64 or 128, lq and lk
+ *     multiples of 128, no dense bias); anything else is refused with a negative code.
+ *   - Limit: shape->b * (lq/128 + lk/128) <= RA_STATIC_MAX_TILES, else -41 and nothing runs.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls share the array, which keeps the previous call's contents.  Each call
+ *     rewrites every entry it later reads, so nothing needs clearing, but calls that
+ *     overlap on the GPU (two streams, two threads) race on it: serialise them.
+ */
+#define RA_STATIC_MAX_TILES 16384
+int ra_fwd_block_static(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_t* k,
+                        const ra_tensor_t* v, const ra_score_mod_t* mod, float* o, float* m,
+                        float* l, int first, void* stream);
+
 /* out = o / l, L = m + log(l): ring.py:134-135.  out has the element type shape->dtype. */
 int ra_fwd_finalize(const ra_shape_t* shape, const float* o, const float* m, const float* l,
                     const ra_tensor_t* out, float* lse, void* stream);

@@ -48,6 +48,8 @@ _SIGNATURES = {
     "ra_device_status": (C.c_int, [_P(C.c_uint32)]),
     "ra_fwd_block": (C.c_int, [_P(RaShape), _P(RaTensor), _P(RaTensor), _P(RaTensor), _P(RaScoreMod),
                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "ra_fwd_block_static": (C.c_int, [_P(RaShape), _P(RaTensor), _P(RaTensor), _P(RaTensor), _P(RaScoreMod),
+                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "ra_fwd_finalize": (C.c_int, [_P(RaShape), C.c_void_p, C.c_void_p, C.c_void_p, _P(RaTensor),
                                   C.c_void_p, C.c_void_p]),
     "ra_bwd_delta": (C.c_int, [_P(RaShape), _P(RaTensor), _P(RaTensor), C.c_void_p, C.c_void_p]),

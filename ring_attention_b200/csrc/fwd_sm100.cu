@@ -508,3 +508,115 @@ cudaError_t tc_fwd_block(const FwdParams& p, cudaStream_t s) {
 }
 
 }  // namespace ra
+
+// -----------------------------------------------------------------------------------------
+// Forward block for callers that must not allocate.
+//
+// tc_fwd_block above takes a few kilobytes of scratch from the stream-ordered allocator for
+// the per-tile mask summaries.  Some hosts cannot afford that: the handler of an XLA / JAX
+// FFI custom call runs while XLA's own allocator holds nearly all of the GPU's memory, so a
+// driver allocation made from inside the handler can fail or stall the device; a serving
+// process that has handed all free memory to its own arena is in the same position.  For
+// them the same kernel is offered with its scratch in a fixed array that is part of the
+// library image: every GPU that loads the library holds these 512 KiB until the process
+// exits, and nothing is allocated or freed by a call.
+//
+// All calls share the one array and it keeps whatever the last call wrote.  The summaries
+// a call needs are completely rewritten by that call's own first two launches, so nothing
+// has to be cleared; but two calls that overlap on the GPU (different streams, or two host
+// threads) overwrite each other's summaries.  Callers must serialise them.
+// -----------------------------------------------------------------------------------------
+namespace ra {
+
+namespace {
+
+constexpr int kStaticMaxTiles = RA_STATIC_MAX_TILES;
+static __device__ __align__(256) TileMeta g_static_tile_meta[kStaticMaxTiles];
+
+constexpr int kMaxDevices = 64;
+
+// Device address of the array on the current device.  The array's name is only a host-side
+// handle for the symbol; the address a kernel can use has to be asked for, once per device,
+// with that device current.
+cudaError_t static_tile_meta(TileMeta** out) {
+  static TileMeta* cache[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  TileMeta* ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_static_tile_meta);
+    if (e != cudaSuccess) return e;
+    if (!sym) return cudaErrorInvalidSymbol;
+    ptr = static_cast<TileMeta*>(sym);
+    __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return cudaSuccess;
+}
+
+}  // namespace
+
+}  // namespace ra
+
+extern "C" int ra_fwd_block_static(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_t* k,
+                                   const ra_tensor_t* v, const ra_score_mod_t* mod, float* o, float* m,
+                                   float* l, int first, void* stream) {
+  using namespace ra;
+  int rc;
+  if ((rc = check_shape(shape))) return rc;
+  if ((rc = check_tensor(q, "q")) || (rc = check_tensor(k, "k")) || (rc = check_tensor(v, "v"))) return rc;
+  if (!o || !m || !l) return fail(-6, "carried state (o, m, l) is NULL");
+  FwdTcParams P;
+  memset(&P, 0, sizeof(P));
+  FwdParams& p = P.p;
+  if ((rc = check_mod(mod, &p.mod))) return rc;
+  p.q = TensorView{q->ptr, q->stride_b, q->stride_l, q->stride_h};
+  p.k = TensorView{k->ptr, k->stride_b, k->stride_l, k->stride_h};
+  p.v = TensorView{v->ptr, v->stride_b, v->stride_l, v->stride_h};
+  p.o = o;
+  p.m = m;
+  p.l = l;
+  p.b = shape->b;
+  p.h = shape->h;
+  p.lq = shape->lq;
+  p.lk = shape->lk;
+  p.dk = shape->dk;
+  p.dv = shape->dv;
+  p.scale = shape->sm_scale;
+  p.first = first ? 1 : 0;
+  if (const char* why = tc_fwd_unsupported_reason(p, shape->dtype))
+    return fail(-40, "ra_fwd_block_static serves only what the tcgen05 forward takes: %s", why);
+  P.n_q_tiles = p.lq / kTileRows;
+  P.n_kv_tiles = p.lk / kTileRows;
+  const long long tiles = (long long)p.b * (P.n_q_tiles + P.n_kv_tiles);
+  if (tiles > kStaticMaxTiles)
+    return fail(-41, "ra_fwd_block_static: b * (lq/128 + lk/128) = %lld tiles exceeds the fixed scratch of %d tiles",
+                tiles, kStaticMaxTiles);
+  const char* why = nullptr;
+  if (!make_tile_map(&P.map_q, p.q, p.b, p.lq, p.h, p.dk, kTileRows, &why) ||
+      !make_tile_map(&P.map_k, p.k, p.b, p.lk, p.h, p.dk, kTileRows, &why) ||
+      !make_tile_map(&P.map_v, p.v, p.b, p.lk, p.h, p.dv, kTileRows, &why))
+    return fail(-42, "ra_fwd_block_static: %s", why);
+  P.status = device_status_word();
+  if (!P.status) return fail(RA_ERR_CUDA, "status word symbol not found");
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e;
+  if (p.mod.kinds & kMaskKinds) {
+    TileMeta* meta = nullptr;
+    if ((e = static_tile_meta(&meta)) != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    TileMeta* mq = meta;
+    TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
+    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess ||
+        (e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s)) != cudaSuccess)
+      return fail_cuda(e, "tile summaries");
+    P.meta_q = mq;
+    P.meta_kv = mk;
+  }
+  e = p.dk == 128 ? launch_fwd<128>(P, s) : launch_fwd<64>(P, s);
+  if (e != cudaSuccess) return fail_cuda(e, "tcgen05 forward block (static scratch)");
+  set_last_impl(RA_IMPL_TCGEN05);
+  return 0;
+}
