@@ -160,24 +160,42 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S^T, dP^T
       constexpr uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);     // dV, dK: B MN-major
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);      // dQ: A and B MN-major
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sdO),
-                     ds_addr = smem_u32(sdS);
-      auto kmajor = [](uint32_t base, int kk) {
-        return make_smem_desc(base + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32, 16, 1024);
-      };
-      auto mnmajor = [](uint32_t base, int kk) { return make_smem_desc(base + kk * 2048, PANEL_BYTES, 1024); };
+      // Low descriptor words: K-major views step 32 B per k-step inside a 64-column panel and one
+      // panel (16 KB) per 4 k-steps; MN-major views step 16 rows (2 KB) per k-step, panels 16 KB apart.
+      constexpr uint32_t kPanel16 = PANEL_BYTES >> 4, kStage16 = TILE_BYTES >> 4;
+      const uint32_t k_km = desc_lo(smem_u32(sK), 16), k_mn = desc_lo(smem_u32(sK), PANEL_BYTES);
+      const uint32_t v_km = desc_lo(smem_u32(sV), 16);
+      const uint32_t q_km = desc_lo(smem_u32(sQ), 16), q_mn = desc_lo(smem_u32(sQ), PANEL_BYTES);
+      const uint32_t do_km = desc_lo(smem_u32(sdO), 16), do_mn = desc_lo(smem_u32(sdO), PANEL_BYTES);
+      const uint32_t ds_km = desc_lo(smem_u32(sdS), 16), ds_mn = desc_lo(smem_u32(sdS), PANEL_BYTES);
+      auto km_off = [](int kk) -> uint32_t { return (kk >> 2) * kPanel16 + (kk & 3) * 2; };
+      auto mn_off = [](int kk) -> uint32_t { return kk * (2048 >> 4); };
       auto issue_s = [&](int stage) {
+        const uint32_t b0 = q_km + stage * kStage16;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem_S, kmajor(k_addr, kk), kmajor(q_addr + stage * TILE_BYTES, kk), idesc_s, kk > 0);
+          mma_ss(tmem_S, desc_from_lo(k_km + km_off(kk)), desc_from_lo(b0 + km_off(kk)), idesc_s, kk > 0);
         tc_commit(&bars[S_FULL]);
       };
       auto issue_dp = [&](int stage) {
+        const uint32_t b0 = do_km + stage * kStage16;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem_dP, kmajor(v_addr, kk), kmajor(do_addr + stage * TILE_BYTES, kk), idesc_s, kk > 0);
+          mma_ss(tmem_dP, desc_from_lo(v_km + km_off(kk)), desc_from_lo(b0 + km_off(kk)), idesc_s, kk > 0);
         tc_commit(&bars[DP_FULL]);
       };
+      auto issue_dv = [&](int stage, bool first_tile) {
+        const uint32_t b0 = do_mn + stage * kStage16;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t pcol = kk < 4 ? kk * 8 : 64 + (kk - 4) * 8;  // P^T columns of the two warpgroups
+          mma_ts(tmem_dV, tmem_S + pcol, desc_from_lo(b0 + mn_off(kk)), idesc_dv, (!first_tile) || kk > 0);
+        }
+      };
+      // Issue order per query tile n (the tensor pipe executes in this order):
+      //   S(n+1) | dQ(n) | dK(n) | dP(n+1) | dV(n+1)
+      // so that the compute warps form P(n+1) under dQ(n)/dK(n), drain dQ(n) under dK(n), and
+      // form dS(n+1) under dV(n+1)/S(n+2).
       bool ok = true;
       int i = next_active(0);
       if (i < P.n_q_tiles) {
@@ -187,39 +205,45 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           tc_fence_after();
           issue_s(0);
           issue_dp(0);
+          ok = mbar_wait(&bars[P_READY], 0, abort_flag, P.status, kStBwdMma);
         }
-        for (int n = 0; ok && i < P.n_q_tiles; ++n) {
+        if (ok) {
+          tc_fence_after();
+          issue_dv(0, true);
+        }
+        for (int n = 0; ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
           const uint32_t par = n & 1;
           const int inext = next_active(i + 1);
-          // dV += P^T dO
-          if (!(ok = mbar_wait(&bars[P_READY], par, abort_flag, P.status, kStBwdMma))) break;
-          tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t pcol = kk < 4 ? kk * 8 : 64 + (kk - 4) * 8;  // P^T columns of the two warpgroups
-            mma_ts(tmem_dV, tmem_S + pcol, mnmajor(do_addr + s * TILE_BYTES, kk), idesc_dv, (n > 0) || kk > 0);
+          const bool has_next = inext < P.n_q_tiles;
+          if (has_next) {
+            if (!(ok = mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma))) break;
+            tc_fence_after();
+            issue_s(sn);
           }
           // dQ = dS K (into the dP^T columns), dK += dS^T Q
           if (!(ok = mbar_wait(&bars[DS_READY], par, abort_flag, P.status, kStBwdMma))) break;
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ss(tmem_dP, mnmajor(ds_addr, kk), mnmajor(k_addr, kk), idesc_dq, kk > 0);
+            mma_ss(tmem_dP, desc_from_lo(ds_mn + mn_off(kk)), desc_from_lo(k_mn + mn_off(kk)), idesc_dq, kk > 0);
           tc_commit(&bars[DQ_FULL]);
+          {
+            const uint32_t b0 = q_mn + s * kStage16;
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ss(tmem_dK, kmajor(ds_addr, kk), mnmajor(q_addr + s * TILE_BYTES, kk), idesc_dv, (n > 0) || kk > 0);
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ss(tmem_dK, desc_from_lo(ds_km + km_off(kk)), desc_from_lo(b0 + mn_off(kk)), idesc_dv,
+                     (n > 0) || kk > 0);
+          }
           tc_commit(&bars[QDO_EMPTY0 + s]);
           tc_commit(&bars[DS_FREE]);
-          if (inext < P.n_q_tiles) {
-            if (!(ok = mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma))) break;
-            tc_fence_after();
-            issue_s(sn);
-            if (!(ok = mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma))) break;
-            tc_fence_after();
-            issue_dp(sn);
-          }
+          if (!has_next) break;
+          if (!(ok = mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma))) break;
+          tc_fence_after();
+          issue_dp(sn);
+          if (!(ok = mbar_wait(&bars[P_READY], par ^ 1, abort_flag, P.status, kStBwdMma))) break;
+          tc_fence_after();
+          issue_dv(sn, false);
           i = inext;
         }
         if (ok) tc_commit(&bars[DKDV_FULL]);
@@ -233,7 +257,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     const int kv_row = kt * kTileRows + r;
     const float scale2 = p.scale * kLog2e;
     const bool alibi = (kinds & RA_MOD_ALIBI) != 0;
-    const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
     int32_t kpos = 0, kseg = 0;
     bool kpre = false;
     if (p.mod.kv_pos) kpos = p.mod.kv_pos[(int64_t)bb * p.lk + kv_row];
@@ -241,89 +264,109 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     if (p.mod.kv_pre) kpre = p.mod.kv_pre[(int64_t)bb * p.lk + kv_row] != 0;
     const int64_t qrow_base = ((int64_t)bb * p.h + hh) * p.lq;
     bool ok = true;
-    int n = 0;
-    for (int i = next_active(0); i < P.n_q_tiles; i = next_active(i + 1), ++n) {
-      const int s = n & 1;
-      const uint32_t par = n & 1;
-      const bool need_mask = masked && tile_class(i) == 2;
-      if (!(ok = mbar_wait(&bars[QDO_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute))) break;
-      const float* Ls = sL + s * kTileRows + g * 64;
-      const float* Dls = sDelta + s * kTileRows + g * 64;
-      // ---- P^T = exp2(S^T * scale2 - L * log2e) on this warpgroup's 64 query columns
-      if (!(ok = mbar_wait(&bars[S_FULL], par, abort_flag, P.status, kStBwdCompute))) break;
-      tc_fence_after();
-      uint32_t sv[2][32];
-      tmem_ld32(tmem_S + lane_off + g * 64, sv[0]);
-      tmem_ld32(tmem_S + lane_off + g * 64 + 32, sv[1]);
-      tc_wait_ld();
-      float pf[64];
-      const int64_t q0 = (int64_t)bb * p.lq + (int64_t)i * kTileRows + g * 64;
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float x = __uint_as_float(sv[c >> 5][c & 31]) * scale2;
-        if (need_mask || alibi) {
-          const int32_t qpos = p.mod.q_pos ? __ldg(p.mod.q_pos + q0 + c) : 0;
-          const int32_t qseg = p.mod.q_seg ? __ldg(p.mod.q_seg + q0 + c) : 0;
-          const bool qpre = p.mod.q_pre ? (__ldg(p.mod.q_pre + q0 + c) != 0) : false;
-          x = apply_mod(x, need_mask ? kinds : (kinds & RA_MOD_ALIBI), p.mod.window, slope2, qpos, qseg, qpre, kpos,
-                        kseg, kpre);
-        }
-        // a masked pair contributes nothing, also on a row whose L is -inf
-        pf[c] = (x == -INFINITY) ? 0.f : ex2(x - Ls[c] * kLog2e);
-      }
-      {
-        uint32_t pk[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) pk[e] = pack_bf16(pf[2 * e], pf[2 * e + 1]);
-        tmem_st32(tmem_S + lane_off + g * 64, pk);  // P^T of warpgroup g: 32 packed columns at S column 64g
-      }
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bars[P_READY]);
-      // ---- dS^T = P^T * (dP^T - delta)
-      if (!(ok = mbar_wait(&bars[DP_FULL], par, abort_flag, P.status, kStBwdCompute))) break;
-      tc_fence_after();
-      tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
-      tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
-      tc_wait_ld();
-      if (!(ok = mbar_wait(&bars[DS_FREE], par ^ 1, abort_flag, P.status, kStBwdCompute))) break;
-      {
+    float pf[64];        // P^T of the tile whose dS^T is formed next (this thread's row, 64 columns)
+    uint32_t sv[2][32];
+    const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
+
+    // One loop body serves every tile so that each phase exists once in the instruction
+    // stream: step k does dS^T(k-1), then P^T(k), then the dQ drain of tile k-1.
+    int i_prev = -1, i_cur = next_active(0);
+    for (int k = 0; ok; ++k) {
+      const bool have_prev = k > 0, have_cur = i_cur < P.n_q_tiles;
+      if (!have_prev && !have_cur) break;
+      if (have_prev) {
+        // ---- dS^T = P^T * (dP^T - delta) of tile k-1 -> shared memory, 128-byte swizzle
+        const int n = k - 1, s = n & 1;
+        const float4* Dls = reinterpret_cast<const float4*>(sDelta + s * kTileRows + g * 64);
+        if (!(ok = mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
+        tc_fence_after();
+        tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
+        tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
+        tc_wait_ld();
+        if (!(ok = mbar_wait(&bars[DS_FREE], (n & 1) ^ 1, abort_flag, P.status, kStBwdCompute))) break;
         uint8_t* row_ptr = sdS + g * PANEL_BYTES + r * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
+          const float4 da = Dls[ch * 2], db = Dls[ch * 2 + 1];
+          const float dl[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = ch * 8 + e * 2;
-            const float d0 = pf[c] * (__uint_as_float(sv[c >> 5][c & 31]) - Dls[c]);
-            const float d1 = pf[c + 1] * (__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - Dls[c + 1]);
+            const float d0 = pf[c] * (__uint_as_float(sv[c >> 5][c & 31]) - dl[e * 2]);
+            const float d1 = pf[c + 1] * (__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - dl[e * 2 + 1]);
             w[e] = pack_bf16(d0, d1);
           }
           *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&bars[DS_READY]);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&bars[DS_READY]);
-      // ---- dQ tile: rows are queries now; add this warpgroup's half of the columns
-      if (!(ok = mbar_wait(&bars[DQ_FULL], par, abort_flag, P.status, kStBwdCompute))) break;
-      tc_fence_after();
-      {
-        constexpr int HALF = D / 2;
-        float* dq_row = p.dq + (qrow_base + (int64_t)i * kTileRows + r) * D + g * HALF;
-#pragma unroll
-        for (int c = 0; c < HALF / 32; ++c) {
-          tmem_ld32(tmem_dP + lane_off + g * HALF + c * 32, sv[0]);
-          tc_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq_row + c * 32 + e, __uint_as_float(sv[0][e]) * p.scale, __uint_as_float(sv[0][e + 1]) * p.scale,
-                       __uint_as_float(sv[0][e + 2]) * p.scale, __uint_as_float(sv[0][e + 3]) * p.scale);
+      if (have_cur) {
+        // ---- P^T = exp2(S^T * scale2 - L * log2e) of tile k on this warpgroup's 64 query columns
+        const int n = k, s = n & 1, i = i_cur;
+        const bool need_mask = masked && tile_class(i) == 2;
+        if (!(ok = mbar_wait(&bars[QDO_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute))) break;
+        const float4* Ls = reinterpret_cast<const float4*>(sL + s * kTileRows + g * 64);
+        if (!(ok = mbar_wait(&bars[S_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
+        tc_fence_after();
+        if (need_mask || alibi) {  // rare: tiles that mix visible and masked pairs, or ALiBi
+          const int64_t q0 = (int64_t)bb * p.lq + (int64_t)i * kTileRows + g * 64;
+          fixup_scores_tmem<false>(tmem_S + lane_off + g * 64, 64, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
+                                   p.mod.window, alibi_over_scale, kpos, kseg, kpre,
+                                   p.mod.q_pos ? p.mod.q_pos + q0 : nullptr, p.mod.q_seg ? p.mod.q_seg + q0 : nullptr,
+                                   p.mod.q_pre ? p.mod.q_pre + q0 : nullptr);
         }
+        tmem_ld32(tmem_S + lane_off + g * 64, sv[0]);
+        tmem_ld32(tmem_S + lane_off + g * 64 + 32, sv[1]);
+        tc_wait_ld();
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 lv = Ls[c4];
+          const float l4[4] = {lv.x, lv.y, lv.z, lv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            // a masked pair (-inf) gives exp2(-inf) = 0; the clamp keeps a row whose L is -inf
+            // (it saw no key) from turning that into exp2(-inf + inf)
+            const float neg_l2 = fminf(-l4[e] * kLog2e, 1e30f);
+            pf[c] = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, neg_l2));
+          }
+        }
+        uint32_t pk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) pk[e] = pack_bf16(pf[2 * e], pf[2 * e + 1]);
+        tmem_st32(tmem_S + lane_off + g * 64, pk);  // P^T of warpgroup g: 32 packed columns at S column 64g
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars[P_READY]);
       }
-      tc_fence_before();
-      mbar_arrive(&bars[DQ_DRAINED]);
+      if (have_prev) {
+        // ---- dQ of tile k-1: rows are queries; add this warpgroup's half of the columns
+        const int n = k - 1;
+        if (!(ok = mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
+        tc_fence_after();
+        constexpr int HALF = D / 2;
+        float* dq_row = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + r) * D + g * HALF;
+#pragma unroll 1
+        for (int c = 0; c < HALF / 8; ++c) {
+          uint32_t a[8];
+          tmem_ld8(tmem_dP + lane_off + g * HALF + c * 8, a);
+          tc_wait_ld();
+          red_add_v4(dq_row + c * 8, __uint_as_float(a[0]) * p.scale, __uint_as_float(a[1]) * p.scale,
+                     __uint_as_float(a[2]) * p.scale, __uint_as_float(a[3]) * p.scale);
+          red_add_v4(dq_row + c * 8 + 4, __uint_as_float(a[4]) * p.scale, __uint_as_float(a[5]) * p.scale,
+                     __uint_as_float(a[6]) * p.scale, __uint_as_float(a[7]) * p.scale);
+        }
+        tc_fence_before();
+        mbar_arrive(&bars[DQ_DRAINED]);
+      }
+      if (!have_cur) break;
+      i_prev = i_cur;
+      i_cur = next_active(i_cur + 1);
     }
+    const int n = (i_prev >= 0) ? 1 : 0;  // whether this CTA had any tile
     // ---- epilogue: dK, dV of this K/V tile
     if (ok && n > 0) ok = mbar_wait(&bars[DKDV_FULL], 0, abort_flag, P.status, kStBwdCompute);
     if (ok && n > 0) {
@@ -332,30 +375,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       const int64_t krow = ((int64_t)bb * p.h + hh) * p.lk + kv_row;
       float* dk_row = p.dk + krow * D + g * HALF;
       float* dv_row = p.dv + krow * D + g * HALF;
-      uint32_t a[32];
-#pragma unroll
-      for (int c = 0; c < HALF / 32; ++c) {
-        tmem_ld32(tmem_dK + lane_off + g * HALF + c * 32, a);
+#pragma unroll 1
+      for (int c = 0; c < HALF / 8; ++c) {
+        uint32_t a[8];
+        tmem_ld8(tmem_dK + lane_off + g * HALF + c * 8, a);
         tc_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 cur = *reinterpret_cast<float4*>(dk_row + c * 32 + e);
+        for (int e = 0; e < 8; e += 4) {
+          float4 cur = *reinterpret_cast<float4*>(dk_row + c * 8 + e);
           cur.x += __uint_as_float(a[e]) * p.scale;
           cur.y += __uint_as_float(a[e + 1]) * p.scale;
           cur.z += __uint_as_float(a[e + 2]) * p.scale;
           cur.w += __uint_as_float(a[e + 3]) * p.scale;
-          *reinterpret_cast<float4*>(dk_row + c * 32 + e) = cur;
+          *reinterpret_cast<float4*>(dk_row + c * 8 + e) = cur;
         }
-        tmem_ld32(tmem_dV + lane_off + g * HALF + c * 32, a);
+        tmem_ld8(tmem_dV + lane_off + g * HALF + c * 8, a);
         tc_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 cur = *reinterpret_cast<float4*>(dv_row + c * 32 + e);
+        for (int e = 0; e < 8; e += 4) {
+          float4 cur = *reinterpret_cast<float4*>(dv_row + c * 8 + e);
           cur.x += __uint_as_float(a[e]);
           cur.y += __uint_as_float(a[e + 1]);
           cur.z += __uint_as_float(a[e + 2]);
           cur.w += __uint_as_float(a[e + 3]);
-          *reinterpret_cast<float4*>(dv_row + c * 32 + e) = cur;
+          *reinterpret_cast<float4*>(dv_row + c * 8 + e) = cur;
         }
       }
     }
@@ -400,6 +443,7 @@ const char* tc_bwd_unsupported_reason(const BwdParams& p, int dtype) {
       (reinterpret_cast<uintptr_t>(p.dq) & 15) || (reinterpret_cast<uintptr_t>(p.dk) & 15) ||
       (reinterpret_cast<uintptr_t>(p.dv) & 15))
     return "lse/delta/dq/dk/dv need 16-byte aligned bases";
+  if (!(p.scale > 0.f)) return "sm_scale must be positive";
   return nullptr;
 }
 

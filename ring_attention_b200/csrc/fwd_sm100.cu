@@ -152,22 +152,25 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
     if (lane == 0 && count > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
-      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      // low descriptor words of the operand tiles; one stage / query tile further is +TILE_BYTES/16
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK), 16);
+      const uint32_t v_lo = desc_lo(smem_u32(sV), PANEL_BYTES);  // V is read MN-major: panels 16 KB apart
       bool ok = true;
       auto issue_s = [&](int t, int stage) {
+        const uint32_t a0 = q_lo + t * (TILE_BYTES >> 4), b0 = k_lo + stage * (TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          mma_ss(tmem_S[t], make_smem_desc(q_addr + t * TILE_BYTES + off, 16, 1024),
-                 make_smem_desc(k_addr + stage * TILE_BYTES + off, 16, 1024), idesc_qk, kk > 0);
+          constexpr int kPanel16 = PANEL_BYTES >> 4;
+          const uint32_t off = (kk >> 2) * kPanel16 + (kk & 3) * 2;
+          mma_ss(tmem_S[t], desc_from_lo(a0 + off), desc_from_lo(b0 + off), idesc_qk, kk > 0);
         }
         tc_commit(&bars[S_FULL0 + t]);
       };
       auto issue_pv = [&](int t, int stage, bool first_tile) {
+        const uint32_t b0 = v_lo + stage * (TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < kTileRows / 16; ++kk)
-          mma_ts(tmem_O[t], tmem_S[t] + kk * 8,
-                 make_smem_desc(v_addr + stage * TILE_BYTES + kk * 2048, PANEL_BYTES, 1024), idesc_pv,
+          mma_ts(tmem_O[t], tmem_S[t] + kk * 8, desc_from_lo(b0 + kk * (2048 >> 4)), idesc_pv,
                  (!first_tile) || kk > 0);
       };
       for (int t = 0; t < ntile && ok; ++t)
@@ -218,46 +221,31 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
     if (p.mod.q_seg) qseg = p.mod.q_seg[(int64_t)bb * p.lq + q_row];
     if (p.mod.q_pre) qpre = p.mod.q_pre[(int64_t)bb * p.lq + q_row] != 0;
     const bool alibi = (kinds & RA_MOD_ALIBI) != 0;
-    const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
     bool ok = true;
 
+    const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
     for (int i = 0; i < count; ++i) {
       const int j = list[i] & 0xFFF;
       const bool need_mask = ((list[i] >> (12 + t)) & 1) != 0;
       if (!(ok = mbar_wait(&bars[S_FULL0 + t], i & 1, abort_flag, P.status, kStFwdSoftmax))) break;
       tc_fence_after();
+      if (need_mask || alibi) {  // rare: tiles that mix visible and masked pairs, or ALiBi
+        const int64_t kv0 = (int64_t)bb * p.lk + (int64_t)j * kTileRows;
+        fixup_scores_tmem<true>(tmem_S[t] + lane_off, kTileRows, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
+                                p.mod.window, alibi_over_scale, qpos, qseg, qpre,
+                                p.mod.kv_pos ? p.mod.kv_pos + kv0 : nullptr, p.mod.kv_seg ? p.mod.kv_seg + kv0 : nullptr,
+                                p.mod.kv_pre ? p.mod.kv_pre + kv0 : nullptr);
+      }
       uint32_t r[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[t] + lane_off + c * 32, r[c]);
       tc_wait_ld();
-      float mx = -INFINITY;
-      if (need_mask || alibi) {
-        const int64_t kv0 = (int64_t)bb * p.lk + (int64_t)j * kTileRows;
+      float mx = -INFINITY;  // raw scores; the scale is positive, so it commutes with max
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = c * 32 + e;
-            const int32_t kpos = p.mod.kv_pos ? __ldg(p.mod.kv_pos + kv0 + col) : 0;
-            const int32_t kseg = p.mod.kv_seg ? __ldg(p.mod.kv_seg + kv0 + col) : 0;
-            const bool kpre = p.mod.kv_pre ? (__ldg(p.mod.kv_pre + kv0 + col) != 0) : false;
-            float x = __uint_as_float(r[c][e]) * scale2;
-            x = apply_mod(x, need_mask ? kinds : (kinds & RA_MOD_ALIBI), p.mod.window, slope2, qpos, qseg, qpre,
-                          kpos, kseg, kpre);
-            r[c][e] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
-          }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float x = __uint_as_float(r[c][e]) * scale2;
-            r[c][e] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
-          }
-      }
-      const float m_new = fmaxf(m_true, mx);
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[c][e]));
+      const float m_new = fmaxf(m_true, mx * scale2);
       m_true = m_new;
       const bool need = (m_new > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
       if (__any_sync(0xffffffffu, need)) {
@@ -266,26 +254,26 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         l_run *= alpha;
         alpha_total *= alpha;
         if (i > 0) {  // O of this tile holds the sum over the tiles before this one
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tmem_O[t] + lane_off + c * 32, o);
+#pragma unroll 1
+          for (int c = 0; c < D / 8; ++c) {
+            uint32_t o[8];
+            tmem_ld8(tmem_O[t] + lane_off + c * 8, o);
             tc_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st32(tmem_O[t] + lane_off + c * 32, o);
+            for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st8(tmem_O[t] + lane_off + c * 8, o);
           }
         }
       }
-      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
       float sum = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2(__uint_as_float(r[c][2 * e]) - m_use);
-          const float p1 = ex2(__uint_as_float(r[c][2 * e + 1]) - m_use);
+          const float p0 = ex2(fmaf(__uint_as_float(r[c][2 * e]), scale2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(r[c][2 * e + 1]), scale2, neg_m));
           sum += p0 + p1;
           pk[e] = pack_bf16(p0, p1);
         }
@@ -305,26 +293,26 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
       const float beta = (m_ref == -INFINITY) ? 1.f : ex2(m_ref - m_true);
       const float in_scale = p.first ? 0.f : alpha_total * beta;
       float* o_row = p.o + state_row * D;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
+#pragma unroll 1
+      for (int c = 0; c < D / 8; ++c) {
+        uint32_t o[8];
         if (count > 0) {
-          tmem_ld32(tmem_O[t] + lane_off + c * 32, o);
+          tmem_ld8(tmem_O[t] + lane_off + c * 8, o);
           tc_wait_ld();
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0u;
+          for (int e = 0; e < 8; ++e) o[e] = 0u;
         }
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
+        for (int e = 0; e < 8; e += 4) {
           float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (!p.first) prev = *reinterpret_cast<const float4*>(o_row + c * 32 + e);
+          if (!p.first) prev = *reinterpret_cast<const float4*>(o_row + c * 8 + e);
           float4 out;
           out.x = __uint_as_float(o[e]) * beta + prev.x * in_scale;
           out.y = __uint_as_float(o[e + 1]) * beta + prev.y * in_scale;
           out.z = __uint_as_float(o[e + 2]) * beta + prev.z * in_scale;
           out.w = __uint_as_float(o[e + 3]) * beta + prev.w * in_scale;
-          *reinterpret_cast<float4*>(o_row + c * 32 + e) = out;
+          *reinterpret_cast<float4*>(o_row + c * 8 + e) = out;
         }
       }
       p.m[state_row] = m_true * (1.f / kLog2e);
@@ -474,6 +462,7 @@ const char* tc_fwd_unsupported_reason(const FwdParams& p, int dtype) {
   if (p.lq / kTileRows > kMaxTiles || p.lk / kTileRows > kMaxTiles) return "more than 4096 tiles along one axis";
   if (p.mod.kinds & RA_MOD_DENSE) return "a dense bias tile is served by the CUDA-core kernels";
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v)) return "q/k/v need 16-byte aligned base and strides";
+  if (!(p.scale > 0.f)) return "sm_scale must be positive";
   return nullptr;
 }
 

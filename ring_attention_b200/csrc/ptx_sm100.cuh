@@ -54,14 +54,18 @@ constexpr long long kWaitCycles = 4000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
+  long long t0 = 0;
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      *abort_flag = 1;
-      atomicOr(status, code);
-      return false;
+    if ((it & 63u) == 0) {  // look at the abort flag and the clock only now and then
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicOr(status, code);
+        return false;
+      }
     }
   }
 }
@@ -161,6 +165,18 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -185,6 +201,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   d |= (uint64_t)2 << 61;  // SWIZZLE_128B
   return d;
 }
+
+// The same descriptor split into its two 32-bit halves.  The high half (SBO = 1024 bytes,
+// version 1, 128-byte swizzle) is one constant for every operand tile of this engine; the
+// low half holds the start address and the leading-dimension offset, so stepping through a
+// tile is one 32-bit add of (byte offset >> 4).  The MMA-issuing thread has a budget of
+// about 64 cycles per instruction: it must not spend them rebuilding 64-bit descriptors.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ uint64_t desc_from_lo(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
 
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {
