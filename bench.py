@@ -54,55 +54,59 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock and throttle reasons while the timed region runs.
+
+    The sampling runs in a separate `nvidia-smi -lms` process: polling NVML from a thread of
+    this process was measured to stretch the timed step (it contends with the launches)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
-        except Exception:
-            self.nv = None
-
-    def _run(self):
-        nv = self.nv
-        names = {
-            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
-            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
-            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                for k, bit in names.items():
-                    if mask & bit:
-                        self.reasons.add(k)
-            except Exception:
-                pass
-            self._stop.wait(0.05)
+        self.index, self.proc, self.path = index, None, None
 
     def __enter__(self):
-        if self.nv is not None:
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
+        import subprocess
+        import tempfile
+
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="ra_clocks_", suffix=".csv")
+            self.out = os.fdopen(fd, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+            time.sleep(0.3)  # let the first sample land before the timed region starts
+        except Exception:
+            self.proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread:
-            self._thread.join()
+        if self.proc is not None:
+            self.proc.terminate()  # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.out.close()
 
     def summary(self):
-        s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+        samples, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 6 or not f[0].isdigit():
+                    continue
+                samples.append(int(f[0]))
+                mx = int(f[1]) if f[1].isdigit() else mx
+                for name, val in zip(self.NAMES, f[2:6]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        s = sorted(samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
                 "samples": len(s)}
 
 
@@ -163,7 +167,7 @@ def workload_config(args, w, n):
         "workload": f"{args.workload}: {w['dtype']} causal MHA fwd+bwd, batch {w['b']}, heads {w['h']}, "
                     f"head_dim {w['d']}, total seq {w['s']} sharded evenly over {n} GPU(s)",
         "global_batch": w["b"], "seq_len": w["s"], "heads": w["h"], "head_dim": w["d"],
-        "parallelism": f"sp{n}", "l2": "inputs larger than L2 (each of q,k,v,dO per rank exceeds 126 MB at N<=2; "
+        "parallelism": f"sp{n}", "layout": args.layout if n > 1 else "contiguous", "l2": "inputs larger than L2 (each of q,k,v,dO per rank exceeds 126 MB at N<=2; "
                                       "an L2 flush runs between steps otherwise)",
     }
 
@@ -176,6 +180,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="causal_32k", choices=list(WORKLOADS))
     ap.add_argument("--block-impl", default="cuda", choices=["cuda", "simt", "tcgen05"])
+    ap.add_argument("--layout", default="zigzag", choices=["zigzag", "contiguous"],
+                    help="token->rank layout at N>1: zigzag balances causal work, contiguous is the reference tests' layout")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -214,7 +220,11 @@ def main():
     g = torch.Generator().manual_seed(1234 + rank)
     host = [torch.randn((b, c, h, d), generator=g).to(dt).pin_memory() for _ in range(4)]
     q, k, v, do = (t.cuda() for t in host)
-    pos = (torch.arange(c, dtype=torch.int32) + rank * c).expand(b, c).contiguous().cuda()
+    if args.layout == "zigzag" and N > 1:
+        pos1 = ra.zigzag_indices(w["s"], rank, N).to(torch.int32)
+    else:
+        pos1 = torch.arange(c, dtype=torch.int32) + rank * c
+    pos = pos1.expand(b, c).contiguous().cuda()
     out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
     lse = torch.empty((b, h, c), dtype=torch.float32, device="cuda")
     mod = RaScoreMod()
@@ -247,15 +257,15 @@ def main():
                 flush.fill_(i)
             evs[i][0].record()
             check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
-            ms, n = ring.last_block_ms()  # synchronises on the call's end: device time of the block kernels
-            fwd_block_ms.append(ms / max(n, 1))
-            exposed_ms.append(ring.last_timing()[1])
             check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
                                   C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
             evs[i][1].record()
-            ms, n = ring.last_block_ms()
+            # device times of this step's block kernels and transfer waits (reads synchronise on the step's end)
+            ms, n = ring.last_block_ms(False)
+            fwd_block_ms.append(ms / max(n, 1))
+            ms, n = ring.last_block_ms(True)
             bwd_block_ms.append(ms / max(n, 1))
-            exposed_ms[-1] += ring.last_timing()[1]
+            exposed_ms.append(ring.last_timing(False)[1] + ring.last_timing(True)[1])
         barrier()
     launches = lib.ra_launch_count() - launches0
     step_ms = sum(a.elapsed_time(b_) for a, b_ in evs) / args.steps
@@ -263,6 +273,11 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     step_ms = float(t.item())
+    exposed_all = [sum(exposed_ms) / len(exposed_ms)]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, exposed_all[0])
+        exposed_all = gathered
     impl_used = {1: "simt", 2: "tcgen05"}.get(lib.ra_last_impl(), "?")
 
     # end to end through the public API, host buffers in and out
@@ -326,8 +341,8 @@ def main():
                 "launch_ms": bwd_ms, "flops_per_launch": bwd_flops_launch,
                 "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
             },
-            "exposed_comm_ms": sum(exposed_ms) / len(exposed_ms),
-            "exposed_comm_frac": (sum(exposed_ms) / len(exposed_ms)) / step_ms,
+            "exposed_comm_ms": max(exposed_all), "exposed_comm_frac": max(exposed_all) / step_ms,
+            "exposed_comm_ms_per_rank": exposed_all,
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
         }

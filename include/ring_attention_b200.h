@@ -208,14 +208,17 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
 int ra_ring_rotate(ra_ring_t* ring, int32_t n, const void* const* src, void* const* dst,
                    const int64_t* nbytes, void* stream);
 
-/* Milliseconds the compute stream spent blocked on transfers during the last
- * ra_ring_fwd / ra_ring_bwd of this handle, and the total time of that call; both need
- * ra_ring_set_timing(ring, 1) and synchronise the stream when read. */
+/* Milliseconds the compute stream spent blocked on transfers during the last forward
+ * (backward == 0) or backward (backward != 0) ring call of this handle, and the total device
+ * time of that call; both need ra_ring_set_timing(ring, 1) and synchronise on the call's end
+ * when read. */
 int ra_ring_set_timing(ra_ring_t* ring, int32_t on);
-int ra_ring_last_timing(ra_ring_t* ring, float* total_ms, float* exposed_comm_ms);
-/* Device time of the block kernels (ra_fwd_block / ra_bwd_block work) launched by the
- * last ring call, summed over its steps, and how many there were (timing must be on). */
-int ra_ring_last_block_ms(ra_ring_t* ring, float* block_ms, int32_t* launches);
+int ra_ring_last_timing(ra_ring_t* ring, int32_t backward, float* total_ms, float* exposed_comm_ms);
+/* Device time of the block kernels (ra_fwd_block / ra_bwd_block work) launched by the last
+ * forward (backward == 0) or backward (backward != 0) ring call of this handle, summed over
+ * its steps, and how many there were.  Timing must be on; the two directions are kept
+ * apart so that a forward + backward step can be queried once, after it ended. */
+int ra_ring_last_block_ms(ra_ring_t* ring, int32_t backward, float* block_ms, int32_t* launches);
 
 #ifdef __cplusplus
 }

@@ -4,10 +4,12 @@
 reference re-exports; the rest is the host plumbing a one-process-per-GPU program needs.
 """
 from ._lib import LIB_PATH, RingAttentionError
+from .layout import zigzag_indices, zigzag_shard, zigzag_unshard
 from .mesh import Mesh, PartitionSpec, Ring
 from .ring import ScoreMod, bwd_block, fwd_block, ring_attention, ring_self_attention
 
 __all__ = [
     "ring_attention", "ring_self_attention", "fwd_block", "bwd_block", "ScoreMod",
     "Mesh", "PartitionSpec", "Ring", "RingAttentionError", "LIB_PATH",
+    "zigzag_indices", "zigzag_shard", "zigzag_unshard",
 ]

@@ -72,8 +72,8 @@ _SIGNATURES = {
     "ra_ring_rotate": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_void_p), _P(C.c_void_p), _P(C.c_int64),
                                  C.c_void_p]),
     "ra_ring_set_timing": (C.c_int, [C.c_void_p, C.c_int32]),
-    "ra_ring_last_timing": (C.c_int, [C.c_void_p, _P(C.c_float), _P(C.c_float)]),
-    "ra_ring_last_block_ms": (C.c_int, [C.c_void_p, _P(C.c_float), _P(C.c_int32)]),
+    "ra_ring_last_timing": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_float), _P(C.c_float)]),
+    "ra_ring_last_block_ms": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_float), _P(C.c_int32)]),
 }
 
 EXPORTS = tuple(_SIGNATURES)

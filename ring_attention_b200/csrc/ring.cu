@@ -138,10 +138,12 @@ struct ra_ring {
   Buffer part[2];  // this rank's dK/dV contribution for a remote block
   Buffer rpart[2]; // a remote rank's contribution for this rank's block
   bool timing = false;
-  std::vector<cudaEvent_t> t_events;  // pairs bracketing each wait on a transfer
-  std::vector<cudaEvent_t> b_events;  // pairs bracketing each block-kernel launch
-  cudaEvent_t t_begin = nullptr, t_end = nullptr;
-  size_t t_used = 0, b_used = 0;
+  // timing, kept per direction ([0] forward call, [1] backward call)
+  std::vector<cudaEvent_t> t_events[2];  // pairs bracketing each wait on a transfer
+  std::vector<cudaEvent_t> b_events[2];  // pairs bracketing each block-kernel launch
+  cudaEvent_t t_begin[2] = {nullptr, nullptr}, t_end[2] = {nullptr, nullptr};
+  size_t t_used[2] = {0, 0}, b_used[2] = {0, 0};
+  int dir = 0;  // direction of the call in progress
 };
 
 namespace {
@@ -210,23 +212,24 @@ int exchange_kv(ra_ring_t* r, const KvMessage& msg, void* stage, int to, int fro
 
 int timing_mark(ra_ring_t* r, cudaStream_t s) {
   if (!r->timing) return 0;
-  if (r->t_used == r->t_events.size()) {
+  const int d = r->dir;
+  if (r->t_used[d] == r->t_events[d].size()) {
     cudaEvent_t e;
     RA_CUDA(cudaEventCreate(&e), "cudaEventCreate");
-    r->t_events.push_back(e);
+    r->t_events[d].push_back(e);
   }
-  RA_CUDA(cudaEventRecord(r->t_events[r->t_used++], s), "cudaEventRecord");
+  RA_CUDA(cudaEventRecord(r->t_events[d][r->t_used[d]++], s), "cudaEventRecord");
   return 0;
 }
 
-int block_mark(ra_ring_t* r, cudaStream_t s) {
+int block_mark(ra_ring_t* r, int dir, cudaStream_t s) {
   if (!r->timing) return 0;
-  if (r->b_used == r->b_events.size()) {
+  if (r->b_used[dir] == r->b_events[dir].size()) {
     cudaEvent_t e;
     RA_CUDA(cudaEventCreate(&e), "cudaEventCreate");
-    r->b_events.push_back(e);
+    r->b_events[dir].push_back(e);
   }
-  RA_CUDA(cudaEventRecord(r->b_events[r->b_used++], s), "cudaEventRecord");
+  RA_CUDA(cudaEventRecord(r->b_events[dir][r->b_used[dir]++], s), "cudaEventRecord");
   return 0;
 }
 
@@ -298,8 +301,9 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
   for (cudaEvent_t* ev : evs)
     if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess)
       return bail(fail_cuda(e, "cudaEventCreate"));
-  if ((e = cudaEventCreate(&r->t_begin)) != cudaSuccess || (e = cudaEventCreate(&r->t_end)) != cudaSuccess)
-    return bail(fail_cuda(e, "cudaEventCreate"));
+  for (int d = 0; d < 2; ++d)
+    if ((e = cudaEventCreate(&r->t_begin[d])) != cudaSuccess || (e = cudaEventCreate(&r->t_end[d])) != cudaSuccess)
+      return bail(fail_cuda(e, "cudaEventCreate"));
   if (nranks > 1) {
     if (!nccl_id) return bail(fail(-34, "nccl_id is NULL with nranks > 1"));
     NcclApi* api = nccl_api();
@@ -322,11 +326,13 @@ int ra_ring_destroy(ra_ring_t* r) {
   }
   cudaEvent_t evs[] = {r->ev_start, r->ev_recv[0], r->ev_recv[1], r->ev_done[0], r->ev_done[1],
                        r->ev_part[0], r->ev_part[1], r->ev_sent[0], r->ev_sent[1], r->ev_tail,
-                       r->t_begin, r->t_end};
+                       r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
   for (cudaEvent_t ev : evs)
     if (ev) cudaEventDestroy(ev);
-  for (cudaEvent_t ev : r->t_events) cudaEventDestroy(ev);
-  for (cudaEvent_t ev : r->b_events) cudaEventDestroy(ev);
+  for (int d = 0; d < 2; ++d) {
+    for (cudaEvent_t ev : r->t_events[d]) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : r->b_events[d]) cudaEventDestroy(ev);
+  }
   if (r->comm_stream) cudaStreamDestroy(r->comm_stream);
   r->state.release();
   r->grads.release();
@@ -348,15 +354,16 @@ int ra_ring_set_timing(ra_ring_t* r, int32_t on) {
   return 0;
 }
 
-int ra_ring_last_timing(ra_ring_t* r, float* total_ms, float* exposed_ms) {
+int ra_ring_last_timing(ra_ring_t* r, int32_t backward, float* total_ms, float* exposed_ms) {
   if (!r) return fail(-30, "ring handle is NULL");
   if (!r->timing) return fail(-35, "timing is off: call ra_ring_set_timing(ring, 1) first");
-  RA_CUDA(cudaEventSynchronize(r->t_end), "cudaEventSynchronize");
+  const int d = backward ? 1 : 0;
+  RA_CUDA(cudaEventSynchronize(r->t_end[d]), "cudaEventSynchronize");
   float tot = 0.f, exp = 0.f;
-  RA_CUDA(cudaEventElapsedTime(&tot, r->t_begin, r->t_end), "cudaEventElapsedTime");
-  for (size_t i = 0; i + 1 < r->t_used; i += 2) {
+  RA_CUDA(cudaEventElapsedTime(&tot, r->t_begin[d], r->t_end[d]), "cudaEventElapsedTime");
+  for (size_t i = 0; i + 1 < r->t_used[d]; i += 2) {
     float ms = 0.f;
-    RA_CUDA(cudaEventElapsedTime(&ms, r->t_events[i], r->t_events[i + 1]), "cudaEventElapsedTime");
+    RA_CUDA(cudaEventElapsedTime(&ms, r->t_events[d][i], r->t_events[d][i + 1]), "cudaEventElapsedTime");
     exp += ms;
   }
   if (total_ms) *total_ms = tot;
@@ -364,18 +371,20 @@ int ra_ring_last_timing(ra_ring_t* r, float* total_ms, float* exposed_ms) {
   return 0;
 }
 
-int ra_ring_last_block_ms(ra_ring_t* r, float* block_ms, int32_t* launches) {
+int ra_ring_last_block_ms(ra_ring_t* r, int32_t backward, float* block_ms, int32_t* launches) {
   if (!r) return fail(-30, "ring handle is NULL");
   if (!r->timing) return fail(-35, "timing is off: call ra_ring_set_timing(ring, 1) first");
-  RA_CUDA(cudaEventSynchronize(r->t_end), "cudaEventSynchronize");
+  const int dir = backward ? 1 : 0;
+  if (r->b_used[dir] == 0) return fail(-38, "no %s call has been timed yet", dir ? "backward" : "forward");
+  RA_CUDA(cudaEventSynchronize(r->t_end[dir]), "cudaEventSynchronize");
   float sum = 0.f;
-  for (size_t i = 0; i + 1 < r->b_used; i += 2) {
+  for (size_t i = 0; i + 1 < r->b_used[dir]; i += 2) {
     float ms = 0.f;
-    RA_CUDA(cudaEventElapsedTime(&ms, r->b_events[i], r->b_events[i + 1]), "cudaEventElapsedTime");
+    RA_CUDA(cudaEventElapsedTime(&ms, r->b_events[dir][i], r->b_events[dir][i + 1]), "cudaEventElapsedTime");
     sum += ms;
   }
   if (block_ms) *block_ms = sum;
-  if (launches) *launches = (int32_t)(r->b_used / 2);
+  if (launches) *launches = (int32_t)(r->b_used[dir] / 2);
   return 0;
 }
 
@@ -421,9 +430,10 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     RA_CUDA(cudaEventRecord(ring->ev_start, stream), "cudaEventRecord");
     RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
   }
-  ring->t_used = 0;
-  ring->b_used = 0;
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin, stream), "cudaEventRecord");
+  ring->dir = 0;
+  ring->t_used[0] = 0;
+  ring->b_used[0] = 0;
+  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin[0], stream), "cudaEventRecord");
 
   const TensorView k_own = p.k, v_own = p.v;
   const ModParams mod_own = p.mod;
@@ -443,16 +453,16 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       if ((rc = wait_transfer(ring, stream, ring->ev_recv[t & 1]))) return rc;
     }
     p.first = (t == 0);
-    if ((rc = block_mark(ring, stream))) return rc;
+    if ((rc = block_mark(ring, 0, stream))) return rc;
     if ((rc = run_fwd_block(p, shape->dtype, stream))) return rc;
-    if ((rc = block_mark(ring, stream))) return rc;
+    if ((rc = block_mark(ring, 0, stream))) return rc;
     if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_done[t & 1], stream), "cudaEventRecord");
   }
   cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, p.o, p.m, p.l,
                                   TensorView{out->ptr, out->stride_b, out->stride_l, out->stride_h},
                                   shape->dtype, lse, stream);
   if (e != cudaSuccess) return fail_cuda(e, "finalize");
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end, stream), "cudaEventRecord");
+  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end[0], stream), "cudaEventRecord");
   return 0;
 }
 
@@ -510,9 +520,10 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     RA_CUDA(cudaEventRecord(ring->ev_start, stream), "cudaEventRecord");
     RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
   }
-  ring->t_used = 0;
-  ring->b_used = 0;
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin, stream), "cudaEventRecord");
+  ring->dir = 1;
+  ring->t_used[1] = 0;
+  ring->b_used[1] = 0;
+  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin[1], stream), "cudaEventRecord");
 
   cudaError_t e = launch_delta(shape->b, shape->h, shape->lq, shape->dv, tv(out), p.dout,
                                shape->dtype, delta, stream);
@@ -539,9 +550,9 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     if (t == 0) {
       p.dk = dk_acc;
       p.dv = dv_acc;
-      if ((rc = block_mark(ring, stream))) return rc;
+      if ((rc = block_mark(ring, 1, stream))) return rc;
       if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
-      if ((rc = block_mark(ring, stream))) return rc;
+      if ((rc = block_mark(ring, 1, stream))) return rc;
       if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_done[0], stream), "cudaEventRecord");
       continue;
     }
@@ -554,9 +565,9 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     p.dv = (float*)((char*)ring->part[slot].ptr + dk_b);
     RA_CUDA(cudaMemsetAsync(ring->part[slot].ptr, 0, dk_b + dv_b, stream), "cudaMemsetAsync");
     count_launch();
-    if ((rc = block_mark(ring, stream))) return rc;
+    if ((rc = block_mark(ring, 1, stream))) return rc;
     if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
-    if ((rc = block_mark(ring, stream))) return rc;
+    if ((rc = block_mark(ring, 1, stream))) return rc;
     RA_CUDA(cudaEventRecord(ring->ev_done[slot], stream), "cudaEventRecord");
     RA_CUDA(cudaEventRecord(ring->ev_part[slot], stream), "cudaEventRecord");
     // send it to the block's owner; receive what another rank computed for our block
@@ -583,7 +594,7 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dk, dk_acc, tv(dk), shape->dtype, stream)) != cudaSuccess ||
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dv, dv_acc, tv(dv), shape->dtype, stream)) != cudaSuccess)
     return fail_cuda(e, "cast");
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end, stream), "cudaEventRecord");
+  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end[1], stream), "cudaEventRecord");
   return 0;
 }
 

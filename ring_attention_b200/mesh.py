@@ -71,14 +71,16 @@ class Ring:
     def set_timing(self, on: bool) -> None:
         check(lib.ra_ring_set_timing(self.handle, int(on)))
 
-    def last_timing(self):
+    def last_timing(self, backward: bool):
+        """(total device ms, ms the compute stream waited on transfers) of the last forward / backward call."""
         tot, exp = C.c_float(), C.c_float()
-        check(lib.ra_ring_last_timing(self.handle, C.byref(tot), C.byref(exp)))
+        check(lib.ra_ring_last_timing(self.handle, int(backward), C.byref(tot), C.byref(exp)))
         return tot.value, exp.value
 
-    def last_block_ms(self):
+    def last_block_ms(self, backward: bool):
+        """(device ms of the block kernels, launches) of the last forward / backward ring call."""
         ms, n = C.c_float(), C.c_int32()
-        check(lib.ra_ring_last_block_ms(self.handle, C.byref(ms), C.byref(n)))
+        check(lib.ra_ring_last_block_ms(self.handle, int(backward), C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
     def destroy(self) -> None:

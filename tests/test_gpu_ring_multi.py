@@ -32,6 +32,9 @@ def _worker(rank, world, port, case, q_out):
         seg = rng.integers(0, 3, (2, max(lq, lk))).astype(np.int32)
         cq, ck = lq // world, lk // world
         sq, sk = slice(rank * cq, (rank + 1) * cq), slice(rank * ck, (rank + 1) * ck)
+        if "zigzag" in mask:  # rank r holds chunks r and 2N-1-r; positions say where each token is
+            sq = ra.zigzag_indices(lq, rank, world).numpy()
+            sk = ra.zigzag_indices(lk, rank, world).numpy()
         qpos = np.broadcast_to(np.arange(lq, dtype=np.int32), (2, lq))
         kpos = np.broadcast_to(np.arange(lk, dtype=np.int32), (2, lk))
         bias, fn, qkw, kkw = None, None, None, None
@@ -73,6 +76,8 @@ CASES = [
     ("float32", 256, 512, 2, 32, "none", "simt"),
     ("bfloat16", 1024, 1024, 2, 128, "causal+seg", "cuda"),
     ("bfloat16", 2048, 2048, 2, 128, "causal", "cuda"),
+    ("bfloat16", 4096, 4096, 2, 128, "causal+zigzag", "tcgen05"),
+    ("bfloat16", 2048, 2048, 2, 64, "causal+seg+zigzag", "tcgen05"),
 ]
 
 

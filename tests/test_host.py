@@ -127,3 +127,23 @@ def test_api_refuses_cpu_tensors_and_unknown_impl():
         ra.ring_attention(q, q, q, "sp")
     with pytest.raises(AssertionError):
         ra.ring_self_attention(q, q, q, None, ("dp", "sp", None), causal=True)  # ring.py:368-370
+
+
+def test_zigzag_layout_round_trip_and_balance():
+    import ring_attention_b200 as ra
+
+    n, S = 4, 64
+    x = torch.arange(2 * S * 3).reshape(2, S, 3)
+    shards = [ra.zigzag_shard(x, r, n) for r in range(n)]
+    assert all(s.shape == (2, S // n, 3) for s in shards)
+    assert torch.equal(ra.zigzag_unshard(shards), x)
+    # every rank sees the same number of causal (query, key) pairs at every step
+    pos = [ra.zigzag_indices(S, r, n) for r in range(n)]
+    for t in range(n):
+        counts = []
+        for r in range(n):
+            src = lib.ra_ring_source(r, n, t)
+            counts.append(int((pos[src][None, :] <= pos[r][:, None]).sum()))
+        assert max(counts) - min(counts) <= S // n, counts
+    with pytest.raises(ValueError):
+        ra.zigzag_indices(30, 0, 4)
