@@ -48,6 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
         "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-I", _nccl_include(),
     ]
+    flags += os.environ.get("RA_EXTRA_NVCC_FLAGS", "").split()
     if verbose:
         flags += ["-Xptxas", "-v"]
 

@@ -13,9 +13,10 @@
 //   dS^T = P^T * (dP^T - delta)       written to shared memory as bf16 (128B swizzle)
 //   dV  += P^T dO         (TS MMA: A from TMEM, B = dO read MN-major) -> TMEM [256,256+D)
 //   dK  += dS^T Q         (SS MMA: B = Q read MN-major)               -> TMEM [256+D,256+2D)
-//   dQ   = dS K           (SS MMA: A = dS^T tile read MN-major, B = K read MN-major)
-//                          -> TMEM [128,128+D), over dP^T, then added to global dQ with
-//                             vector float reductions.
+//   dQ^T = K^T dS^T       (SS MMA: A = K read MN-major, B = dS^T tile read MN-major; head dim 128)
+//                          -> TMEM [128,256), over dP^T; lane = head-dim index, so each warp adds
+//                             128 contiguous bytes of a dQ row to the fp32 accumulator per reduction.
+//                             (head dim 64 forms dQ = dS K instead and uses vector reductions.)
 // warps 0-7: compute (two warpgroups split the 128 query columns), warp 8: TMA producer,
 // warp 9: MMA issuer.
 #include <cstring>
@@ -30,6 +31,27 @@ namespace {
 using namespace ptx;
 
 constexpr int kBwdThreads = 320;
+
+// Optional timeline of one CTA (build with -DRA_TRACE): each TRACE(tag) appends
+// (tag, clock64) to a global buffer.  Used to find where a tile's time goes.
+#ifdef RA_TRACE
+}  // namespace
+__device__ unsigned long long g_trace[4][4096];
+__device__ unsigned int g_trace_n[4];
+namespace {
+#define TRACE(who, tag)                                                        \
+  do {                                                                         \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                          \
+      unsigned int k_ = g_trace_n[who]++;                                      \
+      if (k_ < 2048) {                                                         \
+        g_trace[who][2 * k_] = (tag);                                          \
+        g_trace[who][2 * k_ + 1] = clock64();                                  \
+      }                                                                        \
+    }                                                                          \
+  } while (0)
+#else
+#define TRACE(who, tag) do {} while (0)
+#endif
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdTcParams {
@@ -77,7 +99,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const BwdParams& p = P.p;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int bh_count = p.b * p.h;
   const int bh = blockIdx.x % bh_count;
   const int kt = blockIdx.x / bh_count;  // K/V tile; tile 0 has the most visible queries under a causal mask
@@ -102,7 +124,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
                  tmem_dK = tmem_base + 256 + D;
   const bool bad = *abort_flag != 0;
@@ -156,10 +178,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      // every lane runs this loop; one elected lane issues each instruction
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S^T, dP^T
       constexpr uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);     // dV, dK: B MN-major
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);      // dQ: A and B MN-major
+      // dQ: A and B MN-major.  D = 128 forms dQ^T (M = D, N = 128 queries); D = 64 forms dQ (M = 128 queries, N = D)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D == 128 ? 128 : D, true, true);
       // Low descriptor words: K-major views step 32 B per k-step inside a 64-column panel and one
       // panel (16 KB) per 4 k-steps; MN-major views step 16 rows (2 KB) per k-step, panels 16 KB apart.
       constexpr uint32_t kPanel16 = PANEL_BYTES >> 4, kStage16 = TILE_BYTES >> 4;
@@ -174,22 +198,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         const uint32_t b0 = q_km + stage * kStage16;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem_S, desc_from_lo(k_km + km_off(kk)), desc_from_lo(b0 + km_off(kk)), idesc_s, kk > 0);
-        tc_commit(&bars[S_FULL]);
+          mma_ss_warp(tmem_S, desc_from_lo(k_km + km_off(kk)), desc_from_lo(b0 + km_off(kk)), idesc_s, kk > 0);
+        tc_commit_warp(&bars[S_FULL]);
       };
       auto issue_dp = [&](int stage) {
         const uint32_t b0 = do_km + stage * kStage16;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem_dP, desc_from_lo(v_km + km_off(kk)), desc_from_lo(b0 + km_off(kk)), idesc_s, kk > 0);
-        tc_commit(&bars[DP_FULL]);
+          mma_ss_warp(tmem_dP, desc_from_lo(v_km + km_off(kk)), desc_from_lo(b0 + km_off(kk)), idesc_s, kk > 0);
+        tc_commit_warp(&bars[DP_FULL]);
       };
       auto issue_dv = [&](int stage, bool first_tile) {
         const uint32_t b0 = do_mn + stage * kStage16;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t pcol = kk < 4 ? kk * 8 : 64 + (kk - 4) * 8;  // P^T columns of the two warpgroups
-          mma_ts(tmem_dV, tmem_S + pcol, desc_from_lo(b0 + mn_off(kk)), idesc_dv, (!first_tile) || kk > 0);
+          mma_ts_warp(tmem_dV, tmem_S + pcol, desc_from_lo(b0 + mn_off(kk)), idesc_dv, (!first_tile) || kk > 0);
         }
       };
       // Issue order per query tile n (the tensor pipe executes in this order):
@@ -197,15 +221,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       // so that the compute warps form P(n+1) under dQ(n)/dK(n), drain dQ(n) under dK(n), and
       // form dS(n+1) under dV(n+1)/S(n+2).
       bool ok = true;
-      int i = next_active(0);
+      int i = __shfl_sync(0xffffffffu, next_active(0), 0);
       if (i < P.n_q_tiles) {
-        ok = mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
-             mbar_wait(&bars[QDO_FULL0], 0, abort_flag, P.status, kStBwdMma);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
+                                         mbar_wait(&bars[QDO_FULL0], 0, abort_flag, P.status, kStBwdMma));
         if (ok) {
           tc_fence_after();
           issue_s(0);
           issue_dp(0);
-          ok = mbar_wait(&bars[P_READY], 0, abort_flag, P.status, kStBwdMma);
+          ok = __all_sync(0xffffffffu, mbar_wait(&bars[P_READY], 0, abort_flag, P.status, kStBwdMma));
         }
         if (ok) {
           tc_fence_after();
@@ -214,39 +238,65 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         for (int n = 0; ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
           const uint32_t par = n & 1;
-          const int inext = next_active(i + 1);
+          const int inext = __shfl_sync(0xffffffffu, next_active(i + 1), 0);
           const bool has_next = inext < P.n_q_tiles;
+          TRACE(0, 1);
           if (has_next) {
-            if (!(ok = mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma))) break;
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
             tc_fence_after();
+            TRACE(0, 2);
             issue_s(sn);
           }
+          TRACE(0, 3);
           // dQ = dS K (into the dP^T columns), dK += dS^T Q
-          if (!(ok = mbar_wait(&bars[DS_READY], par, abort_flag, P.status, kStBwdMma))) break;
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_READY], par, abort_flag, P.status, kStBwdMma)))) break;
           tc_fence_after();
+          TRACE(0, 4);
+          if constexpr (D == 128) {
+            // dQ^T = K^T dS^T: lane = head-dim index, column = query, so that a warp's reduction
+            // instruction covers 128 contiguous bytes of one dQ row
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ss(tmem_dP, desc_from_lo(ds_mn + mn_off(kk)), desc_from_lo(k_mn + mn_off(kk)), idesc_dq, kk > 0);
-          tc_commit(&bars[DQ_FULL]);
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ss_warp(tmem_dP, desc_from_lo(k_mn + mn_off(kk)), desc_from_lo(ds_mn + mn_off(kk)), idesc_dq, kk > 0);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ss_warp(tmem_dP, desc_from_lo(ds_mn + mn_off(kk)), desc_from_lo(k_mn + mn_off(kk)), idesc_dq, kk > 0);
+          }
+          tc_commit_warp(&bars[DQ_FULL]);
+#ifdef RA_TRACE_SERIAL
+          TRACE(0, 20);
+          mbar_wait(&bars[DQ_FULL], par, abort_flag, P.status, kStBwdMma);
+          TRACE(0, 21);
+#endif
           {
             const uint32_t b0 = q_mn + s * kStage16;
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)
-              mma_ss(tmem_dK, desc_from_lo(ds_km + km_off(kk)), desc_from_lo(b0 + mn_off(kk)), idesc_dv,
+              mma_ss_warp(tmem_dK, desc_from_lo(ds_km + km_off(kk)), desc_from_lo(b0 + mn_off(kk)), idesc_dv,
                      (n > 0) || kk > 0);
           }
-          tc_commit(&bars[QDO_EMPTY0 + s]);
-          tc_commit(&bars[DS_FREE]);
+          tc_commit_warp(&bars[QDO_EMPTY0 + s]);
+          tc_commit_warp(&bars[DS_FREE]);
+#ifdef RA_TRACE_SERIAL
+          TRACE(0, 22);
+          mbar_wait(&bars[DS_FREE], par, abort_flag, P.status, kStBwdMma);
+          TRACE(0, 23);
+#endif
+          TRACE(0, 5);
           if (!has_next) break;
-          if (!(ok = mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma))) break;
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma)))) break;
           tc_fence_after();
+          TRACE(0, 6);
           issue_dp(sn);
-          if (!(ok = mbar_wait(&bars[P_READY], par ^ 1, abort_flag, P.status, kStBwdMma))) break;
+          TRACE(0, 7);
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[P_READY], par ^ 1, abort_flag, P.status, kStBwdMma)))) break;
           tc_fence_after();
+          TRACE(0, 8);
           issue_dv(sn, false);
           i = inext;
         }
-        if (ok) tc_commit(&bars[DKDV_FULL]);
+        if (ok) tc_commit_warp(&bars[DKDV_FULL]);
       }
     }
   } else {
@@ -278,8 +328,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         // ---- dS^T = P^T * (dP^T - delta) of tile k-1 -> shared memory, 128-byte swizzle
         const int n = k - 1, s = n & 1;
         const float4* Dls = reinterpret_cast<const float4*>(sDelta + s * kTileRows + g * 64);
+        if (threadIdx.x == 0) TRACE(1, 10);
         if (!(ok = mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
         tc_fence_after();
+        if (threadIdx.x == 0) TRACE(1, 11);
         tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
         tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
         tc_wait_ld();
@@ -302,6 +354,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(&bars[DS_READY]);
+        if (threadIdx.x == 0) TRACE(1, 12);
       }
       if (have_cur) {
         // ---- P^T = exp2(S^T * scale2 - L * log2e) of tile k on this warpgroup's 64 query columns
@@ -311,6 +364,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         const float4* Ls = reinterpret_cast<const float4*>(sL + s * kTileRows + g * 64);
         if (!(ok = mbar_wait(&bars[S_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
         tc_fence_after();
+        if (threadIdx.x == 0) TRACE(1, 13);
         if (need_mask || alibi) {  // rare: tiles that mix visible and masked pairs, or ALiBi
           const int64_t q0 = (int64_t)bb * p.lq + (int64_t)i * kTileRows + g * 64;
           fixup_scores_tmem<false>(tmem_S + lane_off + g * 64, 64, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
@@ -341,26 +395,40 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars[P_READY]);
+        if (threadIdx.x == 0) TRACE(1, 14);
       }
       if (have_prev) {
         // ---- dQ of tile k-1: rows are queries; add this warpgroup's half of the columns
         const int n = k - 1;
         if (!(ok = mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
         tc_fence_after();
-        constexpr int HALF = D / 2;
-        float* dq_row = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + r) * D + g * HALF;
-#pragma unroll 1
-        for (int c = 0; c < HALF / 8; ++c) {
-          uint32_t a[8];
-          tmem_ld8(tmem_dP + lane_off + g * HALF + c * 8, a);
+        if (threadIdx.x == 0) TRACE(1, 15);
+        if constexpr (D == 128) {
+          // dQ^T: this thread owns head-dim index r; columns are the tile's queries, this warpgroup's 64
+          float* dq_col = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + g * 64) * D + r;
+          tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
+          tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
           tc_wait_ld();
-          red_add_v4(dq_row + c * 8, __uint_as_float(a[0]) * p.scale, __uint_as_float(a[1]) * p.scale,
-                     __uint_as_float(a[2]) * p.scale, __uint_as_float(a[3]) * p.scale);
-          red_add_v4(dq_row + c * 8 + 4, __uint_as_float(a[4]) * p.scale, __uint_as_float(a[5]) * p.scale,
-                     __uint_as_float(a[6]) * p.scale, __uint_as_float(a[7]) * p.scale);
+          // the values are in registers: hand the TMEM columns back before the reductions, so that
+          // dP^T of the next tile does not wait for them
+          tc_fence_before();
+          mbar_arrive(&bars[DQ_DRAINED]);
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            atomicAdd(dq_col + (int64_t)c * D, __uint_as_float(sv[c >> 5][c & 31]) * p.scale);  // no return value: a RED
+        } else {
+          constexpr int HALF = D / 2;
+          float* dq_row = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + r) * D + g * HALF;
+          tmem_ld32(tmem_dP + lane_off + g * HALF, sv[0]);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4(dq_row + e, __uint_as_float(sv[0][e]) * p.scale, __uint_as_float(sv[0][e + 1]) * p.scale,
+                       __uint_as_float(sv[0][e + 2]) * p.scale, __uint_as_float(sv[0][e + 3]) * p.scale);
+          tc_fence_before();
+          mbar_arrive(&bars[DQ_DRAINED]);
         }
-        tc_fence_before();
-        mbar_arrive(&bars[DQ_DRAINED]);
+        if (threadIdx.x == 0) TRACE(1, 16);
       }
       if (!have_cur) break;
       i_prev = i_cur;
@@ -479,3 +547,12 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
 }
 
 }  // namespace ra
+
+#ifdef RA_TRACE
+extern "C" int ra_debug_trace(unsigned long long* buf, unsigned int* counts) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(buf, ra::g_trace, sizeof(unsigned long long) * 4 * 4096);
+  cudaMemcpyFromSymbol(counts, ra::g_trace_n, sizeof(unsigned int) * 4);
+  return 0;
+}
+#endif

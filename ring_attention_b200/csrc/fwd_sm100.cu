@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
   int* count_slot = reinterpret_cast<int*>(tmem_slot + 2);
 
   const FwdParams& p = P.p;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int bh_count = p.b * p.h;
   const int n_pairs = (P.n_q_tiles + 1) / 2;
   const int bh = blockIdx.x % bh_count;
@@ -115,8 +115,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const int count = *count_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+  const int count = __shfl_sync(0xffffffffu, *count_slot, 0);
   const uint32_t tmem_S[2] = {tmem_base, tmem_base + 128};
   const uint32_t tmem_O[2] = {tmem_base + 256, tmem_base + 256 + D};
 
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && count > 0) {
+    if (count > 0) {  // every lane runs this loop; one elected lane issues each instruction
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       // low descriptor words of the operand tiles; one stage / query tile further is +TILE_BYTES/16
@@ -162,43 +162,43 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         for (int kk = 0; kk < D / 16; ++kk) {
           constexpr int kPanel16 = PANEL_BYTES >> 4;
           const uint32_t off = (kk >> 2) * kPanel16 + (kk & 3) * 2;
-          mma_ss(tmem_S[t], desc_from_lo(a0 + off), desc_from_lo(b0 + off), idesc_qk, kk > 0);
+          mma_ss_warp(tmem_S[t], desc_from_lo(a0 + off), desc_from_lo(b0 + off), idesc_qk, kk > 0);
         }
-        tc_commit(&bars[S_FULL0 + t]);
+        tc_commit_warp(&bars[S_FULL0 + t]);
       };
       auto issue_pv = [&](int t, int stage, bool first_tile) {
         const uint32_t b0 = v_lo + stage * (TILE_BYTES >> 4);
 #pragma unroll
         for (int kk = 0; kk < kTileRows / 16; ++kk)
-          mma_ts(tmem_O[t], tmem_S[t] + kk * 8, desc_from_lo(b0 + kk * (2048 >> 4)), idesc_pv,
+          mma_ts_warp(tmem_O[t], tmem_S[t] + kk * 8, desc_from_lo(b0 + kk * (2048 >> 4)), idesc_pv,
                  (!first_tile) || kk > 0);
       };
       for (int t = 0; t < ntile && ok; ++t)
-        ok = mbar_wait(&bars[Q_FULL0 + t], 0, abort_flag, P.status, kStFwdMma);
-      if (ok) ok = mbar_wait(&bars[K_FULL0], 0, abort_flag, P.status, kStFwdMma);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL0 + t], 0, abort_flag, P.status, kStFwdMma));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars[K_FULL0], 0, abort_flag, P.status, kStFwdMma));
       if (ok) {
         tc_fence_after();
         for (int t = 0; t < ntile; ++t) issue_s(t, 0);
-        tc_commit(&bars[K_EMPTY0]);
+        tc_commit_warp(&bars[K_EMPTY0]);
       }
       for (int i = 0; i < count && ok; ++i) {
         const int s = i & 1, sn = (i + 1) & 1;
         const uint32_t ph = (i >> 1) & 1, phn = ((i + 1) >> 1) & 1;
         const bool has_next = i + 1 < count;
-        if (has_next && !(ok = mbar_wait(&bars[K_FULL0 + sn], phn, abort_flag, P.status, kStFwdMma))) break;
-        if (!(ok = mbar_wait(&bars[V_FULL0 + s], ph, abort_flag, P.status, kStFwdMma))) break;
+        if (has_next && !(ok = __all_sync(0xffffffffu, mbar_wait(&bars[K_FULL0 + sn], phn, abort_flag, P.status, kStFwdMma)))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[V_FULL0 + s], ph, abort_flag, P.status, kStFwdMma)))) break;
         for (int t = 0; t < ntile; ++t) {
-          if (!(ok = mbar_wait(&bars[P_FULL0 + t], i & 1, abort_flag, P.status, kStFwdMma))) break;
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[P_FULL0 + t], i & 1, abort_flag, P.status, kStFwdMma)))) break;
           tc_fence_after();
           issue_pv(t, s, i == 0);
-          if (t == ntile - 1) tc_commit(&bars[V_EMPTY0 + s]);
+          if (t == ntile - 1) tc_commit_warp(&bars[V_EMPTY0 + s]);
           if (has_next) {
             issue_s(t, sn);
-            if (t == ntile - 1) tc_commit(&bars[K_EMPTY0 + sn]);
+            if (t == ntile - 1) tc_commit_warp(&bars[K_EMPTY0 + sn]);
           }
         }
       }
-      if (ok) tc_commit(&bars[O_FULL]);
+      if (ok) tc_commit_warp(&bars[O_FULL]);
     }
   } else if (warp < 4 * ntile) {
     // ------------------------------------------------------------ softmax + epilogue

@@ -111,6 +111,19 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
+// One lane of a converged warp.  The MMA-issuing warp runs its whole loop with all 32 lanes
+// (so that addresses and descriptors are warp-uniform values the compiler can keep in
+// uniform registers) and elects a lane only for the instruction itself.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                        uint32_t accumulate) {
@@ -130,6 +143,19 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// Whole-warp forms: every lane calls them, one elected lane issues.
+__device__ __forceinline__ void mma_ss_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  if (elect_one()) mma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void mma_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  if (elect_one()) mma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void tc_commit_warp(uint64_t* bar) {
+  if (elect_one()) tc_commit(bar);
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base + i).
