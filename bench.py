@@ -75,7 +75,7 @@ class ClockSampler:
             self.out = os.fdopen(fd, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+                 "-lms", "200"], stdout=self.out, stderr=subprocess.DEVNULL)
             time.sleep(0.3)  # let the first sample land before the timed region starts
         except Exception:
             self.proc = None
@@ -249,26 +249,36 @@ def main():
         step()
     barrier()
     launches0 = lib.ra_launch_count()
-    fwd_block_ms, bwd_block_ms, exposed_ms = [], [], []
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush_ms = 0.0
     with ClockSampler(local) as clocks:
+        barrier()
+        # K steps back to back with no host synchronisation in between; the device clock brackets them
+        e_begin.record()
         for i in range(args.steps):
             if flush is not None:
                 flush.fill_(i)
-            evs[i][0].record()
             check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
             check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
                                   C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
-            evs[i][1].record()
-            # device times of this step's block kernels and transfer waits (reads synchronise on the step's end)
-            ms, n = ring.last_block_ms(False)
-            fwd_block_ms.append(ms / max(n, 1))
-            ms, n = ring.last_block_ms(True)
-            bwd_block_ms.append(ms / max(n, 1))
-            exposed_ms.append(ring.last_timing(False)[1] + ring.last_timing(True)[1])
+        e_end.record()
         barrier()
+    if flush is not None:  # the L2 flush writes are not part of a step: time them alone and take them out
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(args.steps):
+            flush.fill_(i)
+        f1.record()
+        torch.cuda.synchronize()
+        flush_ms = f0.elapsed_time(f1) / args.steps
+    # device times of the last step's block kernels and transfer waits (events recorded inside the timed region)
+    ms, n = ring.last_block_ms(False)
+    fwd_block_ms = [ms / max(n, 1)]
+    ms, n = ring.last_block_ms(True)
+    bwd_block_ms = [ms / max(n, 1)]
+    exposed_ms = [ring.last_timing(False)[1] + ring.last_timing(True)[1]]
     launches = lib.ra_launch_count() - launches0
-    step_ms = sum(a.elapsed_time(b_) for a, b_ in evs) / args.steps
+    step_ms = e_begin.elapsed_time(e_end) / args.steps - flush_ms
     t = torch.tensor([step_ms], device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -336,7 +346,10 @@ def main():
             "block_impl": impl_used,
             "roofline": {
                 "bound": "tensor", "kernel": f"{impl_used} backward block", "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "unit": "TFLOP/s", "frac": achieved / peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of this kernel from the ncu capture of the 8k-token
+                # case (profiles/tc_bwd_kernel_causal_8k.md: 3.44 GB), scaled by the visible-pair count of a launch
+                "traffic": (3.44e9 * bwd_flops_launch / 1.3746e12) if impl_used == "tcgen05" else None,
                 "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if bwd_ms > 5 else 'burst'}",
                 "launch_ms": bwd_ms, "flops_per_launch": bwd_flops_launch,
                 "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
