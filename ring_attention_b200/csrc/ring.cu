@@ -6,8 +6,16 @@
 //     a double buffer that the running block kernel is not reading;
 //   * in the backward K/V are fetched the same way, dQ stays at home, and the dK/dV
 //     contribution of a step goes straight to the block's owner, which adds it in fp32.
-// Transfers are NCCL send/recv on a side stream, fenced against the caller's stream
-// with events; nothing here synchronises the host.
+// Two transports:
+//   p2p  (default): the owner PUSHES with copy-engine peer copies (cudaMemcpyAsync into the
+//         consumer's staging buffer, mapped through CUDA IPC) on a high-priority side stream:
+//         no SM is used, so the copy really runs under the block kernel.  Ordering between
+//         GPUs uses 64-bit sequence counters in each rank's flag page, written with release
+//         stores by small kernels after the copy and polled with acquire loads by small
+//         bounded-wait kernels on the stream that needs the data.
+//   nccl: grouped ncclSend / ncclRecv on the side stream (RA_TRANSPORT=nccl).  Its fixed cost
+//         per exchange (~0.4 ms measured at 8 GPUs) is too high for short ring steps.
+// Nothing here synchronises the host, except when staging buffers have to grow.
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -17,6 +25,7 @@
 
 #include "common.cuh"
 #include "host_util.h"
+#include "tc_common.cuh"
 
 namespace ra {
 
@@ -33,6 +42,7 @@ struct NcclApi {
   ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*GroupStart)() = nullptr;
   ncclResult_t (*GroupEnd)() = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -62,6 +72,7 @@ NcclApi* nccl_api() {
   RA_SYM(Recv, "ncclRecv")
   RA_SYM(GroupStart, "ncclGroupStart")
   RA_SYM(GroupEnd, "ncclGroupEnd")
+  RA_SYM(AllGather, "ncclAllGather")
   RA_SYM(GetErrorString, "ncclGetErrorString")
 #undef RA_SYM
   return &api;
@@ -124,19 +135,84 @@ bool is_dense(const TensorView& t, int b, int len, int h, int d) {
 
 }  // namespace ra
 
+
 using namespace ra;
+
+namespace ringimpl {
+
+// Flag page of one rank (64-bit counters, all monotonic over the life of the ring).
+//   KV_READY[slot]   written by the rank that pushed a K/V block into stage[slot]: global step id
+//   PART_READY[slot] written by the rank that pushed a dK/dV contribution into rpart[slot]
+//   PROGRESS[j]      written by rank j: number of block steps j has finished (frees stage slots)
+//   ADDED[j]         written by rank j: global id up to which j has summed received contributions
+constexpr int kMaxRanks = 64;
+constexpr int kFlagKvReady = 0, kFlagPartReady = 2, kFlagProgress = 8, kFlagAdded = 8 + kMaxRanks;
+constexpr int kNumFlags = 8 + 2 * kMaxRanks;
+constexpr uint32_t kStRingWait = 1u << 16;  // status bit: a cross-GPU wait ran out
+
+struct FlagList {
+  uint64_t* ptr[kMaxRanks];
+  int n;
+};
+
+// One thread; waits until *flag >= target.  Bounded: gives up after about two seconds of
+// cycles, records it in the status word and returns, so the stream always drains.
+__global__ void wait_flag_kernel(const uint64_t* flag, uint64_t target, unsigned int* status) {
+  const long long t0 = clock64();
+  while (true) {
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    if (v >= target) return;
+    __nanosleep(100);
+    if (clock64() - t0 > 4000000000LL) {
+      atomicOr(status, kStRingWait);
+      return;
+    }
+  }
+}
+
+// Thread i publishes `value` to list.ptr[i] (own or peer memory) after everything that
+// preceded this kernel on its stream.
+__global__ void set_flags_kernel(FlagList list, uint64_t value) {
+  const int i = threadIdx.x;
+  if (i >= list.n) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(list.ptr[i]), "l"(value) : "memory");
+}
+
+struct IpcBundle {
+  cudaIpcMemHandle_t stage[2], rpart[2], flags;
+};
+
+}  // namespace ringimpl
+using namespace ringimpl;
 
 struct ra_ring {
   int rank = 0, nranks = 1, device = 0;
   ncclComm_t comm = nullptr;
-  cudaStream_t comm_stream = nullptr;
+  cudaStream_t push_stream = nullptr;    // transfers this rank issues (high priority)
+  cudaStream_t reduce_stream = nullptr;  // sums of dK/dV contributions this rank receives (p2p)
   cudaEvent_t ev_start = nullptr, ev_recv[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
   cudaEvent_t ev_part[2] = {nullptr, nullptr}, ev_sent[2] = {nullptr, nullptr}, ev_tail = nullptr;
+  cudaEvent_t ev_push_tail = nullptr, ev_step0 = nullptr;
+  bool p2p = false;
+  // buffers other ranks write into (cudaMalloc'ed, exported through CUDA IPC under p2p)
+  void* stage[2] = {nullptr, nullptr};  // K, V and the kv-side score-mod arrays of a remote block
+  void* rpart[2] = {nullptr, nullptr};  // a remote rank's dK/dV contribution for this rank's block
+  size_t stage_bytes = 0, rpart_bytes = 0;
+  uint64_t* flags = nullptr;
+  struct Peer {
+    void* stage[2] = {nullptr, nullptr};
+    void* rpart[2] = {nullptr, nullptr};
+    uint64_t* flags = nullptr;
+  };
+  std::vector<Peer> peers;  // this process's view of every rank's buffers ([rank] = own pointers)
+  void* ipc_send = nullptr;  // device scratch for the handle all-gather
+  void* ipc_recv = nullptr;
+  uint64_t epoch = 0;  // global step id of the next call's step 0 (advances by nranks per call)
   Buffer state;    // o (fp32), m, l
-  Buffer stage[2]; // K, V and the kv-side score-mod arrays of a remote block
   Buffer grads;    // delta, dq, dk, dv accumulators (fp32)
   Buffer part[2];  // this rank's dK/dV contribution for a remote block
-  Buffer rpart[2]; // a remote rank's contribution for this rank's block
   bool timing = false;
   // timing, kept per direction ([0] forward call, [1] backward call)
   std::vector<cudaEvent_t> t_events[2];  // pairs bracketing each wait on a transfer
@@ -146,7 +222,7 @@ struct ra_ring {
   int dir = 0;  // direction of the call in progress
 };
 
-namespace {
+namespace ringimpl {
 
 struct KvMessage {
   // Flat messages that make up one K/V block: pointers on the sender (own tensors) and
@@ -189,25 +265,15 @@ void use_staged(const KvMessage& msg, void* base, TensorView* k, TensorView* v, 
   if (mod->kv_pre) mod->kv_pre = (const uint8_t*)(p + msg.offset[i++]);
 }
 
-int exchange_kv(ra_ring_t* r, const KvMessage& msg, void* stage, int to, int from) {
-  NcclApi* api = nccl_api();
-  ncclResult_t rc = api->GroupStart();
-  if (rc != ncclSuccess) return fail_nccl(rc, "ncclGroupStart");
-  for (int i = 0; i < msg.n; ++i) {
-    rc = api->Send(msg.src[i], msg.bytes[i], ncclChar, to, r->comm, r->comm_stream);
-    if (rc != ncclSuccess) return fail_nccl(rc, "ncclSend");
-    rc = api->Recv((char*)stage + msg.offset[i], msg.bytes[i], ncclChar, from, r->comm, r->comm_stream);
-    if (rc != ncclSuccess) return fail_nccl(rc, "ncclRecv");
-  }
-  rc = api->GroupEnd();
-  if (rc != ncclSuccess) return fail_nccl(rc, "ncclGroupEnd");
-  return 0;
-}
-
 #define RA_CUDA(call, what)                             \
   do {                                                  \
     cudaError_t e__ = (call);                           \
     if (e__ != cudaSuccess) return fail_cuda(e__, what); \
+  } while (0)
+#define RA_NCCL(call, what)                                  \
+  do {                                                       \
+    ncclResult_t r__ = (call);                               \
+    if (r__ != ncclSuccess) return fail_nccl(r__, what);     \
   } while (0)
 
 int timing_mark(ra_ring_t* r, cudaStream_t s) {
@@ -233,12 +299,185 @@ int block_mark(ra_ring_t* r, int dir, cudaStream_t s) {
   return 0;
 }
 
-// Make the caller's stream wait for a transfer; with timing on, bracket the wait.
+int launch_wait(ra_ring_t* r, cudaStream_t s, int flag_index, uint64_t target) {
+  unsigned int* status = device_status_word();
+  if (!status) return fail(RA_ERR_CUDA, "status word symbol not found");
+  wait_flag_kernel<<<1, 1, 0, s>>>(r->flags + flag_index, target, status);
+  count_launch();
+  RA_CUDA(cudaGetLastError(), "wait_flag_kernel");
+  return 0;
+}
+
+// Publish `value` into flag `flag_index` of one peer (peer >= 0) or of every rank but this one (-1).
+int launch_set(ra_ring_t* r, cudaStream_t s, int peer, int flag_index, uint64_t value) {
+  FlagList list;
+  list.n = 0;
+  for (int j = 0; j < r->nranks; ++j) {
+    if (peer >= 0 ? j != peer : j == r->rank) continue;
+    list.ptr[list.n++] = r->peers[j].flags + flag_index;
+  }
+  if (list.n == 0) return 0;
+  set_flags_kernel<<<1, kMaxRanks, 0, s>>>(list, value);
+  count_launch();
+  RA_CUDA(cudaGetLastError(), "set_flags_kernel");
+  return 0;
+}
+
+// Make the caller's stream wait for an event recorded on a transfer stream; with timing on,
+// bracket the wait.
 int wait_transfer(ra_ring_t* r, cudaStream_t s, cudaEvent_t ev) {
   int rc;
   if ((rc = timing_mark(r, s))) return rc;
   RA_CUDA(cudaStreamWaitEvent(s, ev, 0), "cudaStreamWaitEvent");
   if ((rc = timing_mark(r, s))) return rc;
+  return 0;
+}
+
+void close_peers(ra_ring_t* r) {
+  for (int j = 0; j < (int)r->peers.size(); ++j) {
+    if (j == r->rank) continue;
+    ra_ring::Peer& p = r->peers[j];
+    for (int i = 0; i < 2; ++i) {
+      if (p.stage[i]) cudaIpcCloseMemHandle(p.stage[i]);
+      if (p.rpart[i]) cudaIpcCloseMemHandle(p.rpart[i]);
+      p.stage[i] = p.rpart[i] = nullptr;
+    }
+    if (p.flags) cudaIpcCloseMemHandle(p.flags);
+    p.flags = nullptr;
+  }
+}
+
+// Collective over the ring: all-gathers the IPC handles of this rank's shared buffers and maps
+// every peer's.  Runs at creation and whenever the shared buffers have been re-allocated.
+int exchange_handles(ra_ring_t* r) {
+  NcclApi* api = nccl_api();
+  IpcBundle mine;
+  for (int i = 0; i < 2; ++i) {
+    RA_CUDA(cudaIpcGetMemHandle(&mine.stage[i], r->stage[i]), "cudaIpcGetMemHandle(stage)");
+    RA_CUDA(cudaIpcGetMemHandle(&mine.rpart[i], r->rpart[i]), "cudaIpcGetMemHandle(rpart)");
+  }
+  RA_CUDA(cudaIpcGetMemHandle(&mine.flags, r->flags), "cudaIpcGetMemHandle(flags)");
+  RA_CUDA(cudaMemcpy(r->ipc_send, &mine, sizeof(mine), cudaMemcpyHostToDevice), "cudaMemcpy");
+  RA_NCCL(api->AllGather(r->ipc_send, r->ipc_recv, sizeof(mine), ncclChar, r->comm, r->push_stream), "ncclAllGather");
+  RA_CUDA(cudaStreamSynchronize(r->push_stream), "cudaStreamSynchronize");
+  std::vector<IpcBundle> all(r->nranks);
+  RA_CUDA(cudaMemcpy(all.data(), r->ipc_recv, sizeof(mine) * r->nranks, cudaMemcpyDeviceToHost), "cudaMemcpy");
+  close_peers(r);
+  r->peers.assign(r->nranks, ra_ring::Peer());
+  for (int j = 0; j < r->nranks; ++j) {
+    ra_ring::Peer& p = r->peers[j];
+    if (j == r->rank) {
+      for (int i = 0; i < 2; ++i) {
+        p.stage[i] = r->stage[i];
+        p.rpart[i] = r->rpart[i];
+      }
+      p.flags = r->flags;
+      continue;
+    }
+    for (int i = 0; i < 2; ++i) {
+      RA_CUDA(cudaIpcOpenMemHandle(&p.stage[i], all[j].stage[i], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(stage)");
+      RA_CUDA(cudaIpcOpenMemHandle(&p.rpart[i], all[j].rpart[i], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(rpart)");
+    }
+    void* f = nullptr;
+    RA_CUDA(cudaIpcOpenMemHandle(&f, all[j].flags, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(flags)");
+    p.flags = (uint64_t*)f;
+  }
+  return 0;
+}
+
+// Grow-only: (re)allocates the buffers peers write into.  Every rank makes the same calls
+// with the same shapes, so every rank grows at the same call and meets in exchange_handles.
+int ensure_shared(ra_ring_t* r, size_t stage_need, size_t rpart_need) {
+  if (stage_need <= r->stage_bytes && rpart_need <= r->rpart_bytes) return 0;
+  RA_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  if (r->p2p) close_peers(r);
+  const size_t ns = stage_need > r->stage_bytes ? stage_need : r->stage_bytes;
+  const size_t np = rpart_need > r->rpart_bytes ? rpart_need : r->rpart_bytes;
+  for (int i = 0; i < 2; ++i) {
+    if (r->stage[i]) cudaFree(r->stage[i]);
+    if (r->rpart[i]) cudaFree(r->rpart[i]);
+    r->stage[i] = r->rpart[i] = nullptr;
+    RA_CUDA(cudaMalloc(&r->stage[i], ns > 0 ? ns : 256), "cudaMalloc(stage)");
+    RA_CUDA(cudaMalloc(&r->rpart[i], np > 0 ? np : 256), "cudaMalloc(rpart)");
+  }
+  r->stage_bytes = ns;
+  r->rpart_bytes = np;
+  if (r->p2p) return exchange_handles(r);
+  return 0;
+}
+
+int exchange_kv_nccl(ra_ring_t* r, const KvMessage& msg, void* stage, int to, int from) {
+  NcclApi* api = nccl_api();
+  RA_NCCL(api->GroupStart(), "ncclGroupStart");
+  for (int i = 0; i < msg.n; ++i) {
+    RA_NCCL(api->Send(msg.src[i], msg.bytes[i], ncclChar, to, r->comm, r->push_stream), "ncclSend");
+    RA_NCCL(api->Recv((char*)stage + msg.offset[i], msg.bytes[i], ncclChar, from, r->comm, r->push_stream), "ncclRecv");
+  }
+  RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
+  return 0;
+}
+
+// Issue, on the push stream, the transfer that gives the consumer of step t (t >= 1) this
+// rank's K/V block.  Called while step t-1 is being enqueued, so it runs under step t-1.
+int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
+  const int N = r->nranks, me = r->rank, slot = t & 1;
+  const int to = (me + t) % N, from = ((me - t) % N + N) % N;
+  if (r->p2p) {
+    // the consumer's stage[slot] was last read by its step t-2 (or by its previous call)
+    const uint64_t need = t >= 3 ? r->epoch + t - 1 : r->epoch;
+    int rc;
+    if ((rc = launch_wait(r, r->push_stream, kFlagProgress + to, need))) return rc;
+    for (int i = 0; i < msg.n; ++i)
+      RA_CUDA(cudaMemcpyAsync((char*)r->peers[to].stage[slot] + msg.offset[i], msg.src[i], msg.bytes[i],
+                              cudaMemcpyDeviceToDevice, r->push_stream), "cudaMemcpyAsync(peer K/V)");
+    return launch_set(r, r->push_stream, to, kFlagKvReady + slot, r->epoch + t);
+  }
+  if (t >= 2) RA_CUDA(cudaStreamWaitEvent(r->push_stream, r->ev_done[slot], 0), "cudaStreamWaitEvent");
+  int rc;
+  if ((rc = exchange_kv_nccl(r, msg, r->stage[slot], to, from))) return rc;
+  RA_CUDA(cudaEventRecord(r->ev_recv[slot], r->push_stream), "cudaEventRecord");
+  return 0;
+}
+
+// Make the compute stream wait until the block of step t (t >= 1) has landed in stage[t & 1].
+int wait_kv(ra_ring_t* r, int t, cudaStream_t stream) {
+  if (!r->p2p) return wait_transfer(r, stream, r->ev_recv[t & 1]);
+  int rc;
+  if ((rc = timing_mark(r, stream))) return rc;
+  if ((rc = launch_wait(r, stream, kFlagKvReady + (t & 1), r->epoch + t))) return rc;
+  return timing_mark(r, stream);
+}
+
+// After the block kernel of step t: tell the ranks that may want to overwrite the slot.
+int step_done(ra_ring_t* r, int t, cudaStream_t stream) {
+  if (r->nranks == 1) return 0;
+  if (r->p2p) return launch_set(r, stream, -1, kFlagProgress + r->rank, r->epoch + t + 1);
+  RA_CUDA(cudaEventRecord(r->ev_done[t & 1], stream), "cudaEventRecord");
+  return 0;
+}
+
+int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
+  if (ring->nranks > 1) {
+    // transfers read the caller's K/V: order them after whatever produced those
+    RA_CUDA(cudaEventRecord(ring->ev_start, stream), "cudaEventRecord");
+    RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
+    if (ring->reduce_stream) RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
+  }
+  ring->dir = dir;
+  ring->t_used[dir] = 0;
+  ring->b_used[dir] = 0;
+  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin[dir], stream), "cudaEventRecord");
+  return 0;
+}
+
+int end_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
+  if (ring->nranks > 1) {
+    // the pushes read the caller's tensors: they must be over before the caller may reuse them
+    RA_CUDA(cudaEventRecord(ring->ev_push_tail, ring->push_stream), "cudaEventRecord");
+    RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_push_tail, 0), "cudaStreamWaitEvent");
+    ring->epoch += ring->nranks;
+  }
+  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end[dir], stream), "cudaEventRecord");
   return 0;
 }
 
@@ -258,7 +497,7 @@ int check_ring_call(ra_ring_t* ring, const ra_shape_t* shape, const TensorView& 
   return 0;
 }
 
-}  // namespace
+}  // namespace ringimpl
 
 extern "C" {
 
@@ -294,10 +533,17 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
     ra_ring_destroy(r);
     return code;
   };
-  if ((e = cudaStreamCreateWithFlags(&r->comm_stream, cudaStreamNonBlocking)) != cudaSuccess)
+  // The transfer streams get the highest priority: the block kernels fill every SM with one
+  // CTA each, and the small kernels that order the transfers must not queue behind them.
+  int prio_low = 0, prio_high = 0;
+  if ((e = cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high)) != cudaSuccess)
+    return bail(fail_cuda(e, "cudaDeviceGetStreamPriorityRange"));
+  if ((e = cudaStreamCreateWithPriority(&r->push_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
+      (e = cudaStreamCreateWithPriority(&r->reduce_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaStreamCreate"));
   cudaEvent_t* evs[] = {&r->ev_start, &r->ev_recv[0], &r->ev_recv[1], &r->ev_done[0], &r->ev_done[1],
-                        &r->ev_part[0], &r->ev_part[1], &r->ev_sent[0], &r->ev_sent[1], &r->ev_tail};
+                        &r->ev_part[0], &r->ev_part[1], &r->ev_sent[0], &r->ev_sent[1], &r->ev_tail,
+                        &r->ev_push_tail, &r->ev_step0};
   for (cudaEvent_t* ev : evs)
     if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess)
       return bail(fail_cuda(e, "cudaEventCreate"));
@@ -312,6 +558,16 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
     memcpy(&uid, nccl_id, sizeof(uid));
     ncclResult_t rc = api->CommInitRank(&r->comm, nranks, uid, rank);
     if (rc != ncclSuccess) return bail(fail_nccl(rc, "ncclCommInitRank"));
+    const char* tr = getenv("RA_TRANSPORT");
+    r->p2p = !(tr && strcmp(tr, "nccl") == 0) && nranks <= kMaxRanks;
+    if ((e = cudaMalloc((void**)&r->flags, kNumFlags * sizeof(uint64_t))) != cudaSuccess ||
+        (e = cudaMemset(r->flags, 0, kNumFlags * sizeof(uint64_t))) != cudaSuccess ||
+        (e = cudaMalloc(&r->ipc_send, sizeof(IpcBundle))) != cudaSuccess ||
+        (e = cudaMalloc(&r->ipc_recv, sizeof(IpcBundle) * nranks)) != cudaSuccess ||
+        (e = cudaDeviceSynchronize()) != cudaSuccess)
+      return bail(fail_cuda(e, "cudaMalloc(flags)"));
+    int rc2 = ensure_shared(r, 256, 256);  // maps every peer's flag page (and placeholder buffers)
+    if (rc2) return bail(rc2);
   }
   *out = r;
   return 0;
@@ -319,28 +575,34 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
 
 int ra_ring_destroy(ra_ring_t* r) {
   if (!r) return 0;
-  if (r->comm_stream) cudaStreamSynchronize(r->comm_stream);
+  if (r->push_stream) cudaStreamSynchronize(r->push_stream);
+  if (r->reduce_stream) cudaStreamSynchronize(r->reduce_stream);
+  if (r->p2p) close_peers(r);
   if (r->comm) {
     NcclApi* api = nccl_api();
     if (api) api->CommDestroy(r->comm);
   }
   cudaEvent_t evs[] = {r->ev_start, r->ev_recv[0], r->ev_recv[1], r->ev_done[0], r->ev_done[1],
                        r->ev_part[0], r->ev_part[1], r->ev_sent[0], r->ev_sent[1], r->ev_tail,
-                       r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
+                       r->ev_push_tail, r->ev_step0, r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
   for (cudaEvent_t ev : evs)
     if (ev) cudaEventDestroy(ev);
   for (int d = 0; d < 2; ++d) {
     for (cudaEvent_t ev : r->t_events[d]) cudaEventDestroy(ev);
     for (cudaEvent_t ev : r->b_events[d]) cudaEventDestroy(ev);
   }
-  if (r->comm_stream) cudaStreamDestroy(r->comm_stream);
+  if (r->push_stream) cudaStreamDestroy(r->push_stream);
+  if (r->reduce_stream) cudaStreamDestroy(r->reduce_stream);
   r->state.release();
   r->grads.release();
   for (int i = 0; i < 2; ++i) {
-    r->stage[i].release();
     r->part[i].release();
-    r->rpart[i].release();
+    if (r->stage[i]) cudaFree(r->stage[i]);
+    if (r->rpart[i]) cudaFree(r->rpart[i]);
   }
+  if (r->flags) cudaFree(r->flags);
+  if (r->ipc_send) cudaFree(r->ipc_send);
+  if (r->ipc_recv) cudaFree(r->ipc_recv);
   delete r;
   return 0;
 }
@@ -406,7 +668,7 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   p.k = {k->ptr, k->stride_b, k->stride_l, k->stride_h};
   p.v = {v->ptr, v->stride_b, v->stride_l, v->stride_h};
   if ((rc = check_ring_call(ring, shape, p.k, p.v))) return rc;
-  const int N = ring->nranks, me = ring->rank;
+  const int N = ring->nranks;
   p.b = shape->b;
   p.h = shape->h;
   p.lq = shape->lq;
@@ -423,47 +685,33 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   p.l = (float*)((char*)ring->state.ptr + o_bytes + ml_bytes);
 
   KvMessage msg = make_kv_message(shape, p.k, p.v, p.mod);
-  if (N > 1) {
-    RA_CUDA(ring->stage[0].reserve(msg.total), "cudaMalloc(stage)");
-    RA_CUDA(ring->stage[1].reserve(msg.total), "cudaMalloc(stage)");
-    // transfers read the caller's K/V: order them after whatever produced those
-    RA_CUDA(cudaEventRecord(ring->ev_start, stream), "cudaEventRecord");
-    RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
-  }
-  ring->dir = 0;
-  ring->t_used[0] = 0;
-  ring->b_used[0] = 0;
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin[0], stream), "cudaEventRecord");
+  if (N > 1 && (rc = ensure_shared(ring, msg.total, 0))) return rc;
+  if ((rc = begin_call(ring, 0, stream))) return rc;
 
   const TensorView k_own = p.k, v_own = p.v;
   const ModParams mod_own = p.mod;
   for (int t = 0; t < N; ++t) {
-    if (t + 1 < N) {  // fetch the block of step t+1 while step t computes
-      int slot = (t + 1) & 1;
-      if (t >= 1) RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_done[slot], 0), "cudaStreamWaitEvent");
-      int to = (me + t + 1) % N, from = ((me - t - 1) % N + N) % N;
-      if ((rc = exchange_kv(ring, msg, ring->stage[slot].ptr, to, from))) return rc;
-      RA_CUDA(cudaEventRecord(ring->ev_recv[slot], ring->comm_stream), "cudaEventRecord");
-    }
+    if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;  // runs under step t
     p.k = k_own;
     p.v = v_own;
     p.mod = mod_own;
     if (t > 0) {
-      use_staged(msg, ring->stage[t & 1].ptr, &p.k, &p.v, &p.mod);
-      if ((rc = wait_transfer(ring, stream, ring->ev_recv[t & 1]))) return rc;
+      use_staged(msg, ring->stage[t & 1], &p.k, &p.v, &p.mod);
+      if ((rc = wait_kv(ring, t, stream))) return rc;
     }
     p.first = (t == 0);
     if ((rc = block_mark(ring, 0, stream))) return rc;
     if ((rc = run_fwd_block(p, shape->dtype, stream))) return rc;
     if ((rc = block_mark(ring, 0, stream))) return rc;
-    if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_done[t & 1], stream), "cudaEventRecord");
+    if ((rc = step_done(ring, t, stream))) return rc;
   }
   cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, p.o, p.m, p.l,
                                   TensorView{out->ptr, out->stride_b, out->stride_l, out->stride_h},
                                   shape->dtype, lse, stream);
   if (e != cudaSuccess) return fail_cuda(e, "finalize");
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end[0], stream), "cudaEventRecord");
-  return 0;
+  // no contributions were exchanged in this call: move this rank's ADDED counter to the call's end
+  if (N > 1 && ring->p2p && (rc = launch_set(ring, stream, -1, kFlagAdded + ring->rank, ring->epoch + N))) return rc;
+  return end_call(ring, 0, stream);
 }
 
 int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
@@ -512,18 +760,10 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   float* dv_acc = (float*)(g + delta_b + dq_b + dk_b);
   KvMessage msg = make_kv_message(shape, p.k, p.v, p.mod);
   if (N > 1) {
-    for (int i = 0; i < 2; ++i) {
-      RA_CUDA(ring->stage[i].reserve(msg.total), "cudaMalloc(stage)");
-      RA_CUDA(ring->part[i].reserve(dk_b + dv_b), "cudaMalloc(part)");
-      RA_CUDA(ring->rpart[i].reserve(dk_b + dv_b), "cudaMalloc(rpart)");
-    }
-    RA_CUDA(cudaEventRecord(ring->ev_start, stream), "cudaEventRecord");
-    RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
+    for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(dk_b + dv_b), "cudaMalloc(part)");
+    if ((rc = ensure_shared(ring, msg.total, dk_b + dv_b))) return rc;
   }
-  ring->dir = 1;
-  ring->t_used[1] = 0;
-  ring->b_used[1] = 0;
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin[1], stream), "cudaEventRecord");
+  if ((rc = begin_call(ring, 1, stream))) return rc;
 
   cudaError_t e = launch_delta(shape->b, shape->h, shape->lq, shape->dv, tv(out), p.dout,
                                shape->dtype, delta, stream);
@@ -534,16 +774,11 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   count_launch();
 
   NcclApi* api = N > 1 ? nccl_api() : nullptr;
+  cudaStream_t add_stream = ring->p2p ? ring->reduce_stream : ring->push_stream;
   const TensorView k_own = p.k, v_own = p.v;
   const ModParams mod_own = p.mod;
   for (int t = 0; t < N; ++t) {
-    if (t + 1 < N) {
-      int slot = (t + 1) & 1;
-      if (t >= 1) RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_done[slot], 0), "cudaStreamWaitEvent");
-      int to = (me + t + 1) % N, from = ((me - t - 1) % N + N) % N;
-      if ((rc = exchange_kv(ring, msg, ring->stage[slot].ptr, to, from))) return rc;
-      RA_CUDA(cudaEventRecord(ring->ev_recv[slot], ring->comm_stream), "cudaEventRecord");
-    }
+    if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;
     p.k = k_own;
     p.v = v_own;
     p.mod = mod_own;
@@ -553,12 +788,16 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       if ((rc = block_mark(ring, 1, stream))) return rc;
       if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
       if ((rc = block_mark(ring, 1, stream))) return rc;
-      if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_done[0], stream), "cudaEventRecord");
+      if ((rc = step_done(ring, 0, stream))) return rc;
+      if (N > 1 && ring->p2p) {  // the sums of received contributions start after the own block's
+        RA_CUDA(cudaEventRecord(ring->ev_step0, stream), "cudaEventRecord");
+        RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_step0, 0), "cudaStreamWaitEvent");
+      }
       continue;
     }
     const int slot = t & 1;
-    use_staged(msg, ring->stage[slot].ptr, &p.k, &p.v, &p.mod);
-    if ((rc = wait_transfer(ring, stream, ring->ev_recv[slot]))) return rc;
+    use_staged(msg, ring->stage[slot], &p.k, &p.v, &p.mod);
+    if ((rc = wait_kv(ring, t, stream))) return rc;
     // this step's contribution to the remote block's dK/dV, built from zero
     if (t >= 3) RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
     p.dk = (float*)ring->part[slot].ptr;
@@ -568,34 +807,41 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     if ((rc = block_mark(ring, 1, stream))) return rc;
     if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
     if ((rc = block_mark(ring, 1, stream))) return rc;
-    RA_CUDA(cudaEventRecord(ring->ev_done[slot], stream), "cudaEventRecord");
+    if ((rc = step_done(ring, t, stream))) return rc;
     RA_CUDA(cudaEventRecord(ring->ev_part[slot], stream), "cudaEventRecord");
-    // send it to the block's owner; receive what another rank computed for our block
-    RA_CUDA(cudaStreamWaitEvent(ring->comm_stream, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
-    int owner = ((me - t) % N + N) % N, giver = (me + t) % N;
-    ncclResult_t nr = api->GroupStart();
-    if (nr != ncclSuccess) return fail_nccl(nr, "ncclGroupStart");
-    nr = api->Send(ring->part[slot].ptr, dk_b + dv_b, ncclChar, owner, ring->comm, ring->comm_stream);
-    if (nr != ncclSuccess) return fail_nccl(nr, "ncclSend");
-    nr = api->Recv(ring->rpart[slot].ptr, dk_b + dv_b, ncclChar, giver, ring->comm, ring->comm_stream);
-    if (nr != ncclSuccess) return fail_nccl(nr, "ncclRecv");
-    nr = api->GroupEnd();
-    if (nr != ncclSuccess) return fail_nccl(nr, "ncclGroupEnd");
-    RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->comm_stream), "cudaEventRecord");
-    e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot].ptr, (int64_t)((dk_b + dv_b) / 4),
-                       ring->comm_stream);
+    // give it to the block's owner; take what another rank computed for this rank's block
+    RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
+    const int owner = ((me - t) % N + N) % N, giver = (me + t) % N;
+    if (ring->p2p) {
+      // the owner's rpart[slot] is free once it has summed the contribution of step t-2
+      const uint64_t need = t >= 3 ? ring->epoch + t - 1 : ring->epoch;
+      if ((rc = launch_wait(ring, ring->push_stream, kFlagAdded + owner, need))) return rc;
+      RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
+                              cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
+      if ((rc = launch_set(ring, ring->push_stream, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
+      RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
+      // owner side, on the reduce stream
+      if ((rc = launch_wait(ring, ring->reduce_stream, kFlagPartReady + slot, ring->epoch + t))) return rc;
+    } else {
+      RA_NCCL(api->GroupStart(), "ncclGroupStart");
+      RA_NCCL(api->Send(ring->part[slot].ptr, dk_b + dv_b, ncclChar, owner, ring->comm, ring->push_stream), "ncclSend");
+      RA_NCCL(api->Recv(ring->rpart[slot], dk_b + dv_b, ncclChar, giver, ring->comm, ring->push_stream), "ncclRecv");
+      RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
+      RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
+    }
+    e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot], (int64_t)((dk_b + dv_b) / 4), add_stream);
     if (e != cudaSuccess) return fail_cuda(e, "add");
+    if (ring->p2p && (rc = launch_set(ring, ring->reduce_stream, -1, kFlagAdded + me, ring->epoch + t + 1))) return rc;
   }
   if (N > 1) {
-    RA_CUDA(cudaEventRecord(ring->ev_tail, ring->comm_stream), "cudaEventRecord");
+    RA_CUDA(cudaEventRecord(ring->ev_tail, add_stream), "cudaEventRecord");
     if ((rc = wait_transfer(ring, stream, ring->ev_tail))) return rc;
   }
   if ((e = launch_cast_from_f32(shape->b, shape->h, shape->lq, shape->dk, dq_acc, tv(dq), shape->dtype, stream)) != cudaSuccess ||
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dk, dk_acc, tv(dk), shape->dtype, stream)) != cudaSuccess ||
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dv, dv_acc, tv(dv), shape->dtype, stream)) != cudaSuccess)
     return fail_cuda(e, "cast");
-  if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end[1], stream), "cudaEventRecord");
-  return 0;
+  return end_call(ring, 1, stream);
 }
 
 int ra_ring_rotate(ra_ring_t* ring, int32_t n, const void* const* src, void* const* dst,
@@ -611,17 +857,13 @@ int ra_ring_rotate(ra_ring_t* ring, int32_t n, const void* const* src, void* con
   }
   NcclApi* api = nccl_api();
   const int N = ring->nranks, to = (ring->rank + 1) % N, from = (ring->rank + N - 1) % N;
-  ncclResult_t nr = api->GroupStart();
-  if (nr != ncclSuccess) return fail_nccl(nr, "ncclGroupStart");
+  RA_NCCL(api->GroupStart(), "ncclGroupStart");
   for (int i = 0; i < n; ++i) {
     if (nbytes[i] <= 0) continue;
-    nr = api->Send(src[i], (size_t)nbytes[i], ncclChar, to, ring->comm, stream);
-    if (nr != ncclSuccess) return fail_nccl(nr, "ncclSend");
-    nr = api->Recv(dst[i], (size_t)nbytes[i], ncclChar, from, ring->comm, stream);
-    if (nr != ncclSuccess) return fail_nccl(nr, "ncclRecv");
+    RA_NCCL(api->Send(src[i], (size_t)nbytes[i], ncclChar, to, ring->comm, stream), "ncclSend");
+    RA_NCCL(api->Recv(dst[i], (size_t)nbytes[i], ncclChar, from, ring->comm, stream), "ncclRecv");
   }
-  nr = api->GroupEnd();
-  if (nr != ncclSuccess) return fail_nccl(nr, "ncclGroupEnd");
+  RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
   return 0;
 }
 
