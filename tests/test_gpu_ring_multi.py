@@ -27,6 +27,8 @@ def _worker(rank, world, port, case, q_out):
         from tests.util import check_close, make_inputs, to_dev
 
         dtype, lq, lk, h, d, mask, impl = case
+        if "nccl" in mask:  # the NCCL send/recv transport instead of the default peer copies
+            os.environ["RA_TRANSPORT"] = "nccl"
         dtype = getattr(torch, dtype)
         q, k, v, do, rng = make_inputs(5, 2, lq, lk, h, d, dtype)
         seg = rng.integers(0, 3, (2, max(lq, lk))).astype(np.int32)
@@ -78,6 +80,7 @@ CASES = [
     ("bfloat16", 2048, 2048, 2, 128, "causal", "cuda"),
     ("bfloat16", 4096, 4096, 2, 128, "causal+zigzag", "tcgen05"),
     ("bfloat16", 2048, 2048, 2, 64, "causal+seg+zigzag", "tcgen05"),
+    ("bfloat16", 2048, 2048, 2, 128, "causal+zigzag+nccl", "tcgen05"),
 ]
 
 
