@@ -443,31 +443,68 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       const int64_t krow = ((int64_t)bb * p.h + hh) * p.lk + kv_row;
       float* dk_row = p.dk + krow * D + g * HALF;
       float* dv_row = p.dv + krow * D + g * HALF;
+      const bool direct = p.dk_out.ptr != nullptr;  // ring of one: results go out in the input dtype
+      __nv_bfloat16* dk_o = direct ? (__nv_bfloat16*)p.dk_out.ptr + (int64_t)bb * p.dk_out.sb +
+                                         (int64_t)kv_row * p.dk_out.sl + (int64_t)hh * p.dk_out.sh + g * HALF
+                                   : nullptr;
+      __nv_bfloat16* dv_o = direct ? (__nv_bfloat16*)p.dv_out.ptr + (int64_t)bb * p.dv_out.sb +
+                                         (int64_t)kv_row * p.dv_out.sl + (int64_t)hh * p.dv_out.sh + g * HALF
+                                   : nullptr;
 #pragma unroll 1
       for (int c = 0; c < HALF / 8; ++c) {
         uint32_t a[8];
         tmem_ld8(tmem_dK + lane_off + g * HALF + c * 8, a);
         tc_wait_ld();
+        if (direct) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(a[0]) * p.scale, __uint_as_float(a[1]) * p.scale);
+          w.y = pack_bf16(__uint_as_float(a[2]) * p.scale, __uint_as_float(a[3]) * p.scale);
+          w.z = pack_bf16(__uint_as_float(a[4]) * p.scale, __uint_as_float(a[5]) * p.scale);
+          w.w = pack_bf16(__uint_as_float(a[6]) * p.scale, __uint_as_float(a[7]) * p.scale);
+          *reinterpret_cast<uint4*>(dk_o + c * 8) = w;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 8; e += 4) {
-          float4 cur = *reinterpret_cast<float4*>(dk_row + c * 8 + e);
-          cur.x += __uint_as_float(a[e]) * p.scale;
-          cur.y += __uint_as_float(a[e + 1]) * p.scale;
-          cur.z += __uint_as_float(a[e + 2]) * p.scale;
-          cur.w += __uint_as_float(a[e + 3]) * p.scale;
-          *reinterpret_cast<float4*>(dk_row + c * 8 + e) = cur;
+          for (int e = 0; e < 8; e += 4) {
+            float4 cur = *reinterpret_cast<float4*>(dk_row + c * 8 + e);
+            cur.x += __uint_as_float(a[e]) * p.scale;
+            cur.y += __uint_as_float(a[e + 1]) * p.scale;
+            cur.z += __uint_as_float(a[e + 2]) * p.scale;
+            cur.w += __uint_as_float(a[e + 3]) * p.scale;
+            *reinterpret_cast<float4*>(dk_row + c * 8 + e) = cur;
+          }
         }
         tmem_ld8(tmem_dV + lane_off + g * HALF + c * 8, a);
         tc_wait_ld();
+        if (direct) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(a[0]), __uint_as_float(a[1]));
+          w.y = pack_bf16(__uint_as_float(a[2]), __uint_as_float(a[3]));
+          w.z = pack_bf16(__uint_as_float(a[4]), __uint_as_float(a[5]));
+          w.w = pack_bf16(__uint_as_float(a[6]), __uint_as_float(a[7]));
+          *reinterpret_cast<uint4*>(dv_o + c * 8) = w;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 8; e += 4) {
-          float4 cur = *reinterpret_cast<float4*>(dv_row + c * 8 + e);
-          cur.x += __uint_as_float(a[e]);
-          cur.y += __uint_as_float(a[e + 1]);
-          cur.z += __uint_as_float(a[e + 2]);
-          cur.w += __uint_as_float(a[e + 3]);
-          *reinterpret_cast<float4*>(dv_row + c * 8 + e) = cur;
+          for (int e = 0; e < 8; e += 4) {
+            float4 cur = *reinterpret_cast<float4*>(dv_row + c * 8 + e);
+            cur.x += __uint_as_float(a[e]);
+            cur.y += __uint_as_float(a[e + 1]);
+            cur.z += __uint_as_float(a[e + 2]);
+            cur.w += __uint_as_float(a[e + 3]);
+            *reinterpret_cast<float4*>(dv_row + c * 8 + e) = cur;
+          }
         }
+      }
+    } else if (ok && n == 0 && p.dk_out.ptr != nullptr) {
+      // no query tile sees this K/V tile: its gradients are zero, and in direct mode nobody else writes them
+      constexpr int HALF = D / 2;
+      __nv_bfloat16* dk_o = (__nv_bfloat16*)p.dk_out.ptr + (int64_t)bb * p.dk_out.sb + (int64_t)kv_row * p.dk_out.sl +
+                            (int64_t)hh * p.dk_out.sh + g * HALF;
+      __nv_bfloat16* dv_o = (__nv_bfloat16*)p.dv_out.ptr + (int64_t)bb * p.dv_out.sb + (int64_t)kv_row * p.dv_out.sl +
+                            (int64_t)hh * p.dv_out.sh + g * HALF;
+#pragma unroll 1
+      for (int c = 0; c < HALF / 8; ++c) {
+        *reinterpret_cast<uint4*>(dk_o + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dv_o + c * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
   }
@@ -512,6 +549,8 @@ const char* tc_bwd_unsupported_reason(const BwdParams& p, int dtype) {
       (reinterpret_cast<uintptr_t>(p.dv) & 15))
     return "lse/delta/dq/dk/dv need 16-byte aligned bases";
   if (!(p.scale > 0.f)) return "sm_scale must be positive";
+  if (p.dk_out.ptr && (!aligned16(p.dk_out) || !p.dv_out.ptr || !aligned16(p.dv_out)))
+    return "dk/dv results need 16-byte aligned bases and strides";
   return nullptr;
 }
 

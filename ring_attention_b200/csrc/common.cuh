@@ -36,6 +36,11 @@ struct FwdParams {
   int32_t b, h, lq, lk, dk, dv;
   float scale;
   int32_t first;
+  // Optional, honoured by the tcgen05 kernel only: when final_out.ptr is set this is the last
+  // block of the attention, and the kernel writes out = o / l (input dtype) and L = m + log l
+  // (ring.py:134-135) itself instead of storing the carried state.
+  TensorView final_out;
+  float* final_lse;
 };
 
 struct BwdParams {
@@ -48,6 +53,10 @@ struct BwdParams {
   float* dv;           // [b,h,lk,dv] fp32, += per call
   int32_t b, h, lq, lk, dk_dim, dv_dim;
   float scale;
+  // Optional, honoured by the tcgen05 kernel only: when dk_out.ptr is set this call is the
+  // whole backward for these keys (ring of one) and the kernel stores dK, dV in the input
+  // dtype straight to the result tensors; dk / dv above are then not touched.
+  TensorView dk_out, dv_out;
 };
 
 // Launchers implemented in the .cu files.  Each returns a cudaError_t.

@@ -293,6 +293,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
       const float beta = (m_ref == -INFINITY) ? 1.f : ex2(m_ref - m_true);
       const float in_scale = p.first ? 0.f : alpha_total * beta;
       float* o_row = p.o + state_row * D;
+      const bool finalize = p.final_out.ptr != nullptr;
+      const float l_tot = l_run * beta;
+      const float inv_l = 1.f / l_tot;  // l = 0 (a row that saw no key) gives 0 * inf = NaN, as o / l does
+      __nv_bfloat16* out_row = finalize ? (__nv_bfloat16*)p.final_out.ptr + (int64_t)bb * p.final_out.sb +
+                                              (int64_t)q_row * p.final_out.sl + (int64_t)hh * p.final_out.sh
+                                        : nullptr;
 #pragma unroll 1
       for (int c = 0; c < D / 8; ++c) {
         uint32_t o[8];
@@ -303,20 +309,34 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
 #pragma unroll
           for (int e = 0; e < 8; ++e) o[e] = 0u;
         }
+        float val[8];
 #pragma unroll
         for (int e = 0; e < 8; e += 4) {
           float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
           if (!p.first) prev = *reinterpret_cast<const float4*>(o_row + c * 8 + e);
-          float4 out;
-          out.x = __uint_as_float(o[e]) * beta + prev.x * in_scale;
-          out.y = __uint_as_float(o[e + 1]) * beta + prev.y * in_scale;
-          out.z = __uint_as_float(o[e + 2]) * beta + prev.z * in_scale;
-          out.w = __uint_as_float(o[e + 3]) * beta + prev.w * in_scale;
-          *reinterpret_cast<float4*>(o_row + c * 8 + e) = out;
+          val[e] = __uint_as_float(o[e]) * beta + prev.x * in_scale;
+          val[e + 1] = __uint_as_float(o[e + 1]) * beta + prev.y * in_scale;
+          val[e + 2] = __uint_as_float(o[e + 2]) * beta + prev.z * in_scale;
+          val[e + 3] = __uint_as_float(o[e + 3]) * beta + prev.w * in_scale;
+        }
+        if (finalize) {
+          uint4 w;
+          w.x = pack_bf16(val[0] * inv_l, val[1] * inv_l);
+          w.y = pack_bf16(val[2] * inv_l, val[3] * inv_l);
+          w.z = pack_bf16(val[4] * inv_l, val[5] * inv_l);
+          w.w = pack_bf16(val[6] * inv_l, val[7] * inv_l);
+          *reinterpret_cast<uint4*>(out_row + c * 8) = w;
+        } else {
+          *reinterpret_cast<float4*>(o_row + c * 8) = make_float4(val[0], val[1], val[2], val[3]);
+          *reinterpret_cast<float4*>(o_row + c * 8 + 4) = make_float4(val[4], val[5], val[6], val[7]);
         }
       }
-      p.m[state_row] = m_true * (1.f / kLog2e);
-      p.l[state_row] = l_run * beta;
+      if (finalize) {
+        if (p.final_lse) p.final_lse[state_row] = m_true * (1.f / kLog2e) + logf(l_tot);
+      } else {
+        p.m[state_row] = m_true * (1.f / kLog2e);
+        p.l[state_row] = l_tot;
+      }
     }
   }
 
@@ -463,6 +483,7 @@ const char* tc_fwd_unsupported_reason(const FwdParams& p, int dtype) {
   if (p.mod.kinds & RA_MOD_DENSE) return "a dense bias tile is served by the CUDA-core kernels";
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v)) return "q/k/v need 16-byte aligned base and strides";
   if (!(p.scale > 0.f)) return "sm_scale must be positive";
+  if (p.final_out.ptr && !aligned16(p.final_out)) return "out needs a 16-byte aligned base and strides";
   return nullptr;
 }
 

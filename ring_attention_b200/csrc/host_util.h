@@ -8,6 +8,7 @@ int fail(int code, const char* fmt, ...);
 int fail_cuda(cudaError_t e, const char* what);
 int current_impl();
 void set_last_impl(int impl);
+int last_impl();
 
 int check_shape(const ra_shape_t* s);
 int check_tensor(const ra_tensor_t* t, const char* name);

@@ -30,6 +30,7 @@ int fail_cuda(cudaError_t e, const char* what) {
 }
 int current_impl() { return g_impl; }
 void set_last_impl(int impl) { g_last_impl = impl; }
+int last_impl() { return g_last_impl; }
 
 static TensorView view(const ra_tensor_t* t) {
   return TensorView{t->ptr, t->stride_b, t->stride_l, t->stride_h};

@@ -690,6 +690,7 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
 
   const TensorView k_own = p.k, v_own = p.v;
   const ModParams mod_own = p.mod;
+  const TensorView out_view{out->ptr, out->stride_b, out->stride_l, out->stride_h};
   for (int t = 0; t < N; ++t) {
     if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;  // runs under step t
     p.k = k_own;
@@ -700,15 +701,20 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       if ((rc = wait_kv(ring, t, stream))) return rc;
     }
     p.first = (t == 0);
+    if (t == N - 1) {  // the tensor-core kernel normalises and writes out / L itself on the last block
+      p.final_out = out_view;
+      p.final_lse = lse;
+    }
     if ((rc = block_mark(ring, 0, stream))) return rc;
     if ((rc = run_fwd_block(p, shape->dtype, stream))) return rc;
     if ((rc = block_mark(ring, 0, stream))) return rc;
     if ((rc = step_done(ring, t, stream))) return rc;
   }
-  cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, p.o, p.m, p.l,
-                                  TensorView{out->ptr, out->stride_b, out->stride_l, out->stride_h},
-                                  shape->dtype, lse, stream);
-  if (e != cudaSuccess) return fail_cuda(e, "finalize");
+  if (last_impl() != RA_IMPL_TCGEN05) {  // the CUDA-core kernel stored the carried state: ring.py:134-135 here
+    cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, p.o, p.m, p.l, out_view,
+                                    shape->dtype, lse, stream);
+    if (e != cudaSuccess) return fail_cuda(e, "finalize");
+  }
   // no contributions were exchanged in this call: move this rank's ADDED counter to the call's end
   if (N > 1 && ring->p2p && (rc = launch_set(ring, stream, -1, kFlagAdded + ring->rank, ring->epoch + N))) return rc;
   return end_call(ring, 0, stream);
@@ -770,8 +776,35 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   if (e != cudaSuccess) return fail_cuda(e, "delta");
   p.delta = delta;
   p.dq = dq_acc;
-  RA_CUDA(cudaMemsetAsync(dq_acc, 0, dq_b + dk_b + dv_b, stream), "cudaMemsetAsync");
+  // Ring of one on the tensor-core path: the kernel stores dK, dV in the result dtype itself, so
+  // their fp32 accumulators are neither cleared nor converted.
+  p.dk = dk_acc;
+  p.dv = dv_acc;
+  bool direct = false;
+  if (N == 1 && current_impl() != RA_IMPL_SIMT) {
+    p.dk_out = tv(dk);
+    p.dv_out = tv(dv);
+    direct = tc_bwd_unsupported_reason(p, shape->dtype) == nullptr;
+    if (!direct) p.dk_out = p.dv_out = TensorView{nullptr, 0, 0, 0};
+  }
+  RA_CUDA(cudaMemsetAsync(dq_acc, 0, direct ? dq_b : dq_b + dk_b + dv_b, stream), "cudaMemsetAsync");
   count_launch();
+  if (direct) {
+    if ((rc = block_mark(ring, 1, stream))) return rc;
+    e = tc_bwd_block(p, stream);
+    if (e == cudaSuccess) {
+      set_last_impl(RA_IMPL_TCGEN05);
+      if ((rc = block_mark(ring, 1, stream))) return rc;
+      if ((e = launch_cast_from_f32(shape->b, shape->h, shape->lq, shape->dk, dq_acc, tv(dq), shape->dtype, stream)) != cudaSuccess)
+        return fail_cuda(e, "cast");
+      return end_call(ring, 1, stream);
+    }
+    if (e != cudaErrorNotSupported) return fail_cuda(e, "tcgen05 backward block");
+    // the driver refused a tensor map: take the general path below
+    ring->b_used[1] = 0;
+    p.dk_out = p.dv_out = TensorView{nullptr, 0, 0, 0};
+    RA_CUDA(cudaMemsetAsync(dk_acc, 0, dk_b + dv_b, stream), "cudaMemsetAsync");
+  }
 
   NcclApi* api = N > 1 ? nccl_api() : nullptr;
   cudaStream_t add_stream = ring->p2p ? ring->reduce_stream : ring->push_stream;
