@@ -19,6 +19,7 @@
 //                             (head dim 64 forms dQ = dS K instead and uses vector reductions.)
 // warps 0-7: compute (two warpgroups split the 128 query columns), warp 8: TMA producer,
 // warp 9: MMA issuer.
+#include <cstdio>
 #include <cstring>
 
 #include "host_util.h"
@@ -221,6 +222,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       // so that the compute warps form P(n+1) under dQ(n)/dK(n), drain dQ(n) under dK(n), and
       // form dS(n+1) under dV(n+1)/S(n+2).
       bool ok = true;
+#ifdef RA_PROF
+      long long pw[5] = {0, 0, 0, 0, 0}, pt0 = clock64(), pa;
+      int ptiles = 0;
+#define PROF_BEGIN() pa = clock64()
+#define PROF_END(slot) pw[slot] += clock64() - pa
+#else
+#define PROF_BEGIN() do {} while (0)
+#define PROF_END(slot) do {} while (0)
+#endif
       int i = __shfl_sync(0xffffffffu, next_active(0), 0);
       if (i < P.n_q_tiles) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
@@ -242,14 +252,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           const bool has_next = inext < P.n_q_tiles;
           TRACE(0, 1);
           if (has_next) {
+            PROF_BEGIN();
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
+            PROF_END(0);
             tc_fence_after();
             TRACE(0, 2);
             issue_s(sn);
           }
           TRACE(0, 3);
           // dQ = dS K (into the dP^T columns), dK += dS^T Q
+          PROF_BEGIN();
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_READY], par, abort_flag, P.status, kStBwdMma)))) break;
+          PROF_END(1);
           tc_fence_after();
           TRACE(0, 4);
           if constexpr (D == 128) {
@@ -285,12 +299,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 #endif
           TRACE(0, 5);
           if (!has_next) break;
+          PROF_BEGIN();
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma)))) break;
+          PROF_END(2);
           tc_fence_after();
           TRACE(0, 6);
           issue_dp(sn);
           TRACE(0, 7);
+          PROF_BEGIN();
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[P_READY], par ^ 1, abort_flag, P.status, kStBwdMma)))) break;
+          PROF_END(3);
+#ifdef RA_PROF
+          ++ptiles;
+#endif
           tc_fence_after();
           TRACE(0, 8);
           issue_dv(sn, false);
@@ -298,6 +319,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         }
         if (ok) tc_commit_warp(&bars[DKDV_FULL]);
       }
+#ifdef RA_PROF
+      if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == 300) && ptiles > 0) {
+        const long long tot = clock64() - pt0;
+        printf("bwd CTA %d: %d tiles, %lld clk/tile; MMA warp waits per tile: QDO_FULL %lld, DS_READY %lld, DQ_DRAINED %lld, P_READY %lld; issuing+other %lld\n",
+               blockIdx.x, ptiles, tot / ptiles, pw[0] / ptiles, pw[1] / ptiles, pw[2] / ptiles, pw[3] / ptiles,
+               (tot - pw[0] - pw[1] - pw[2] - pw[3]) / ptiles);
+      }
+#endif
     }
   } else {
     // ------------------------------------------------------------ compute (warps 0-7)
