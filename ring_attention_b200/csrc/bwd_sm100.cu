@@ -65,7 +65,7 @@ struct BwdTcParams {
 };
 
 enum Bar {
-  KV_FULL = 0, QDO_FULL0, QDO_FULL1, QDO_EMPTY0, QDO_EMPTY1, S_FULL, DP_FULL, P_READY, DS_READY, DS_FREE,
+  KV_FULL = 0, Q_FULL0, Q_FULL1, Q_EMPTY0, Q_EMPTY1, DO_FULL0, DO_FULL1, DO_EMPTY0, DO_EMPTY1, S_FULL, DP_FULL, P_READY, DS_READY, DS_FREE,
   DQ_FULL, DQ_DRAINED, DKDV_FULL, NUM_BARS
 };
 
@@ -160,21 +160,48 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           tma_load_4d(sV + pn * PANEL_BYTES, &P.map_v, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
         }
       }
+      // Two streams of loads: Q (with L and delta of its rows) and dO.  A Q stage is free after
+      // dK of its tile, a dO stage already after dV of its tile, one MMA group earlier in the
+      // next iteration: dO runs further ahead.  The lane polls both streams so that neither
+      // blocks the other.
       const int64_t row_base = ((int64_t)bb * p.h + hh) * p.lq;
-      for (int n = 0; i < P.n_q_tiles; i = next_active(i + 1), ++n) {
-        const int s = n & 1;
-        const uint32_t ph = (n >> 1) & 1;
-        if (!mbar_wait(&bars[QDO_EMPTY0 + s], ph ^ 1, abort_flag, P.status, kStBwdProducer)) break;
-        mbar_arrive_expect_tx(&bars[QDO_FULL0 + s], 2 * TILE_BYTES + 2 * kTileRows * 4);
-        for (int pn = 0; pn < PANELS; ++pn) {
-          tma_load_4d(sQ + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_q, &bars[QDO_FULL0 + s], pn * 64, hh,
-                      i * kTileRows, bb);
-          tma_load_4d(sdO + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_do, &bars[QDO_FULL0 + s], pn * 64, hh,
-                      i * kTileRows, bb);
+      int qi = i, doi = i, qn = 0, don = 0;
+      long long t0 = 0;
+      uint32_t idle = 0;
+      while (qi < P.n_q_tiles || doi < P.n_q_tiles) {
+        bool moved = false;
+        if (qi < P.n_q_tiles && mbar_test(&bars[Q_EMPTY0 + (qn & 1)], ((qn >> 1) & 1) ^ 1)) {
+          const int s = qn & 1;
+          mbar_arrive_expect_tx(&bars[Q_FULL0 + s], TILE_BYTES + 2 * kTileRows * 4);
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_4d(sQ + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_q, &bars[Q_FULL0 + s], pn * 64, hh, qi * kTileRows, bb);
+          bulk_load(sL + s * kTileRows, p.lse + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
+          bulk_load(sDelta + s * kTileRows, p.delta + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
+          qi = next_active(qi + 1);
+          ++qn;
+          moved = true;
         }
-        bulk_load(sL + s * kTileRows, p.lse + row_base + (int64_t)i * kTileRows, kTileRows * 4, &bars[QDO_FULL0 + s]);
-        bulk_load(sDelta + s * kTileRows, p.delta + row_base + (int64_t)i * kTileRows, kTileRows * 4,
-                  &bars[QDO_FULL0 + s]);
+        if (doi < P.n_q_tiles && mbar_test(&bars[DO_EMPTY0 + (don & 1)], ((don >> 1) & 1) ^ 1)) {
+          const int s = don & 1;
+          mbar_arrive_expect_tx(&bars[DO_FULL0 + s], TILE_BYTES);
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_4d(sdO + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_do, &bars[DO_FULL0 + s], pn * 64, hh, doi * kTileRows, bb);
+          doi = next_active(doi + 1);
+          ++don;
+          moved = true;
+        }
+        if (moved) {
+          t0 = 0;
+        } else if ((++idle & 63u) == 0) {  // bounded polling
+          if (*abort_flag) break;
+          const long long now = clock64();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            atomicOr(P.status, kStBwdProducer);
+            break;
+          }
+        }
       }
     }
   } else if (warp == 9) {
@@ -234,7 +261,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       int i = __shfl_sync(0xffffffffu, next_active(0), 0);
       if (i < P.n_q_tiles) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
-                                         mbar_wait(&bars[QDO_FULL0], 0, abort_flag, P.status, kStBwdMma));
+                                         mbar_wait(&bars[Q_FULL0], 0, abort_flag, P.status, kStBwdMma) &&
+                                         mbar_wait(&bars[DO_FULL0], 0, abort_flag, P.status, kStBwdMma));
         if (ok) {
           tc_fence_after();
           issue_s(0);
@@ -244,6 +272,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         if (ok) {
           tc_fence_after();
           issue_dv(0, true);
+          tc_commit_warp(&bars[DO_EMPTY0]);
         }
         for (int n = 0; ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
@@ -253,7 +282,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           TRACE(0, 1);
           if (has_next) {
             PROF_BEGIN();
-            if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[QDO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
             PROF_END(0);
             tc_fence_after();
             TRACE(0, 2);
@@ -290,7 +319,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
               mma_ss_warp(tmem_dK, desc_from_lo(ds_km + km_off(kk)), desc_from_lo(b0 + mn_off(kk)), idesc_dv,
                      (n > 0) || kk > 0);
           }
-          tc_commit_warp(&bars[QDO_EMPTY0 + s]);
+          tc_commit_warp(&bars[Q_EMPTY0 + s]);
           tc_commit_warp(&bars[DS_FREE]);
 #ifdef RA_TRACE_SERIAL
           TRACE(0, 22);
@@ -302,6 +331,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           PROF_BEGIN();
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma)))) break;
           PROF_END(2);
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
           tc_fence_after();
           TRACE(0, 6);
           issue_dp(sn);
@@ -315,6 +345,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           tc_fence_after();
           TRACE(0, 8);
           issue_dv(sn, false);
+          tc_commit_warp(&bars[DO_EMPTY0 + sn]);
           i = inext;
         }
         if (ok) tc_commit_warp(&bars[DKDV_FULL]);
@@ -322,7 +353,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 #ifdef RA_PROF
       if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == 300) && ptiles > 0) {
         const long long tot = clock64() - pt0;
-        printf("bwd CTA %d: %d tiles, %lld clk/tile; MMA warp waits per tile: QDO_FULL %lld, DS_READY %lld, DQ_DRAINED %lld, P_READY %lld; issuing+other %lld\n",
+        printf("bwd CTA %d: %d tiles, %lld clk/tile; MMA warp waits per tile: Q_FULL %lld, DS_READY %lld, DQ_DRAINED %lld, P_READY %lld; issuing+other %lld\n",
                blockIdx.x, ptiles, tot / ptiles, pw[0] / ptiles, pw[1] / ptiles, pw[2] / ptiles, pw[3] / ptiles,
                (tot - pw[0] - pw[1] - pw[2] - pw[3]) / ptiles);
       }
@@ -389,7 +420,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         // ---- P^T = exp2(S^T * scale2 - L * log2e) of tile k on this warpgroup's 64 query columns
         const int n = k, s = n & 1, i = i_cur;
         const bool need_mask = masked && tile_class(i) == 2;
-        if (!(ok = mbar_wait(&bars[QDO_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute))) break;
+        if (!(ok = mbar_wait(&bars[Q_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute))) break;
         const float4* Ls = reinterpret_cast<const float4*>(sL + s * kTileRows + g * 64);
         if (!(ok = mbar_wait(&bars[S_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
         tc_fence_after();
