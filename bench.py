@@ -76,7 +76,12 @@ class ClockSampler:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-lms", "200"], stdout=self.out, stderr=subprocess.DEVNULL)
-            time.sleep(0.3)  # let the first sample land before the timed region starts
+            # nvidia-smi's start-up (driver queries over every GPU of the box) was seen to stall the
+            # device for tens of ms: wait for its first sample before the timed region starts
+            t_end = time.time() + 10.0
+            while time.time() < t_end and os.path.getsize(self.path) == 0 and self.proc.poll() is None:
+                time.sleep(0.05)
+            time.sleep(0.1)
         except Exception:
             self.proc = None
         return self
