@@ -6,6 +6,9 @@ Workload (default `causal_32k`): bf16 causal self-attention, forward + backward,
 16 heads, head dim 128, 32768 tokens in total, sharded evenly over the N GPUs of the ring
 (strong scaling), Q/K/V/dO ~ N(0,1) from a seeded generator, softmax scale 1/sqrt(128).
 One step = one ring forward + one ring backward.  Prints ONE JSON line on rank 0.
+Other workloads (`--workload`): `documents_128k` (document mask, causal inside a document),
+`alibi_window_64k` (ALiBi bias + causal window of 4096 tokens, head dim 64, forward only),
+`causal_1m` (131072 tokens per GPU, weak scaling: 1 Mi tokens at 8 GPUs).
 
 `value` times the C-ABI ring calls with inputs resident in HBM; `e2e` times the public
 Python API (`ring_attention` + autograd backward) with inputs in pinned host memory, the
@@ -32,17 +35,54 @@ WORKLOADS = {
     "causal_32k": dict(dtype="bf16", b=2, h=16, d=128, s=32768, mask="causal"),
     "config1_fp32": dict(dtype="f32", b=1, h=4, d=64, s=1024, mask="causal"),
     "causal_8k": dict(dtype="bf16", b=2, h=16, d=128, s=8192, mask="causal"),
+    # documents of seeded lengths U[512, 16384] packed until the sequence is full; a pair is visible
+    # inside one document, causally
+    "documents_128k": dict(dtype="bf16", b=1, h=32, d=128, s=131072, mask="documents"),
+    # ALiBi slopes 2^(-8(h+1)/16), visible iff 0 <= q_pos - kv_pos < 4096; forward only
+    "alibi_window_64k": dict(dtype="bf16", b=4, h=16, d=64, s=65536, mask="alibi+window", window=4096, backward=False),
+    # 131072 tokens per GPU (1 Mi tokens at 8 GPUs), inputs ~ N(0, 0.5^2)
+    "causal_1m": dict(dtype="bf16", b=1, h=8, d=128, s_per_gpu=131072, mask="causal", std=0.5),
 }
-METRIC = "ring_attention_fwd_bwd_tokens_per_s"
+
+
+def metric_name(w):
+    return "ring_attention_fwd_bwd_tokens_per_s" if w.get("backward", True) else "ring_attention_fwd_tokens_per_s"
 
 
 def causal_pairs(s):
     return s * (s + 1) // 2
 
 
+def document_lengths(s, seed=0):
+    """Seeded packing: lengths uniform in [512, 16384] until `s` tokens are filled, the last one cut."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    out, left = [], s
+    while left > 0:
+        n = min(int(rng.integers(512, 16385)), left)
+        out.append(n)
+        left -= n
+    return out
+
+
+def visible_pairs(w):
+    """Exact number of visible (query, key) pairs of one batch element and head."""
+    s = w["s"]
+    if w["mask"] == "causal":
+        return causal_pairs(s)
+    if w["mask"] == "documents":
+        return sum(causal_pairs(n) for n in document_lengths(s))
+    if w["mask"] == "alibi+window":
+        win = min(w["window"], s)
+        return causal_pairs(win) + (s - win) * win
+    raise ValueError(w["mask"])
+
+
 def flops(w, fwd=True, bwd=True):
+    bwd = bwd and w.get("backward", True)
     per_pair = (4 * w["d"] if fwd else 0) + (10 * w["d"] if bwd else 0)
-    return w["b"] * w["h"] * causal_pairs(w["s"]) * per_pair
+    return w["b"] * w["h"] * visible_pairs(w) * per_pair
 
 
 def peaks():
@@ -154,9 +194,9 @@ def run_reference(args, w):
     base["value"] = v
     ms = w["b"] * w["s"] / v * 1e3
     line = {
-        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(w), "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak" if "s_per_gpu" in w else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, w, args.gpus),
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -168,9 +208,11 @@ def run_reference(args, w):
 
 
 def workload_config(args, w, n):
+    what = {"causal": "causal", "documents": "document-masked (causal inside a document)",
+            "alibi+window": f"ALiBi + causal window {w.get('window', 0)}"}[w["mask"]]
     return {
-        "workload": f"{args.workload}: {w['dtype']} causal MHA fwd+bwd, batch {w['b']}, heads {w['h']}, "
-                    f"head_dim {w['d']}, total seq {w['s']} sharded evenly over {n} GPU(s)",
+        "workload": f"{args.workload}: {w['dtype']} {what} MHA {'fwd+bwd' if w.get('backward', True) else 'fwd'}, "
+                    f"batch {w['b']}, heads {w['h']}, head_dim {w['d']}, total seq {w['s']} sharded evenly over {n} GPU(s)",
         "global_batch": w["b"], "seq_len": w["s"], "heads": w["h"], "head_dim": w["d"],
         "parallelism": f"sp{n}", "layout": args.layout if n > 1 else "contiguous", "l2": "inputs larger than L2 (each of q,k,v,dO per rank exceeds 126 MB at N<=2; "
                                       "an L2 flush runs between steps otherwise)",
@@ -190,7 +232,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if "s_per_gpu" in w:
+        w["s"] = w["s_per_gpu"] * args.gpus
+    backward = w.get("backward", True)
     if args.impl == "reference":
         return run_reference(args, w)
 
@@ -223,18 +268,30 @@ def main():
 
     # synthetic inputs, pinned on the host (e2e) and resident on the device (value)
     g = torch.Generator().manual_seed(1234 + rank)
-    host = [torch.randn((b, c, h, d), generator=g).to(dt).pin_memory() for _ in range(4)]
+    host = [(torch.randn((b, c, h, d), generator=g) * w.get("std", 1.0)).to(dt).pin_memory() for _ in range(4)]
     q, k, v, do = (t.cuda() for t in host)
     if args.layout == "zigzag" and N > 1:
-        pos1 = ra.zigzag_indices(w["s"], rank, N).to(torch.int32)
+        idx = ra.zigzag_indices(w["s"], rank, N)
     else:
-        pos1 = torch.arange(c, dtype=torch.int32) + rank * c
-    pos = pos1.expand(b, c).contiguous().cuda()
+        idx = torch.arange(c) + rank * c
+    pos = idx.to(torch.int32).expand(b, c).contiguous().cuda()
     out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
     lse = torch.empty((b, h, c), dtype=torch.float32, device="cuda")
     mod = RaScoreMod()
     mod.kinds = _lib.RA_MOD_CAUSAL
     mod.q_pos = mod.kv_pos = pos.data_ptr()
+    seg = slopes = None
+    if w["mask"] == "documents":
+        lens = torch.tensor(document_lengths(w["s"]))
+        seg_global = torch.repeat_interleave(torch.arange(len(lens)), lens)
+        seg = seg_global[idx].to(torch.int32).expand(b, c).contiguous().cuda()
+        mod.kinds |= _lib.RA_MOD_SEGMENT
+        mod.q_seg = mod.kv_seg = seg.data_ptr()
+    elif w["mask"] == "alibi+window":
+        slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / h) for i in range(h)], dtype=torch.float32, device="cuda")
+        mod.kinds |= _lib.RA_MOD_ALIBI | _lib.RA_MOD_WINDOW
+        mod.window = w["window"]
+        mod.alibi_slopes = slopes.data_ptr()
     sh = RaShape(b, h, c, c, d, d, dcode, 1 / math.sqrt(d))
     tv = lambda t: C.byref(RaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2)))
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -242,8 +299,9 @@ def main():
 
     def step():
         check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
-        check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
-                              C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
+        if backward:
+            check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
+                                  C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
 
     def barrier():
         if world > 1:
@@ -263,9 +321,7 @@ def main():
         for i in range(args.steps):
             if flush is not None:
                 flush.fill_(i)
-            check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
-            check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do),
-                                  C.byref(mod), tv(dq), tv(dk), tv(dv), stream))
+            step()
         e_end.record()
         barrier()
     if flush is not None:  # the L2 flush writes are not part of a step: time them alone and take them out
@@ -279,9 +335,9 @@ def main():
     # device times of the last step's block kernels and transfer waits (events recorded inside the timed region)
     ms, n = ring.last_block_ms(False)
     fwd_block_ms = [ms / max(n, 1)]
-    ms, n = ring.last_block_ms(True)
+    ms, n = ring.last_block_ms(True) if backward else (0.0, 1)
     bwd_block_ms = [ms / max(n, 1)]
-    exposed_ms = [ring.last_timing(False)[1] + ring.last_timing(True)[1]]
+    exposed_ms = [ring.last_timing(False)[1] + (ring.last_timing(True)[1] if backward else 0.0)]
     launches = lib.ra_launch_count() - launches0
     step_ms = e_begin.elapsed_time(e_end) / args.steps - flush_ms
     t = torch.tensor([step_ms], device="cuda")
@@ -298,20 +354,25 @@ def main():
     # end to end through the public API, host buffers in and out
     e2e = None
     if not args.no_e2e:
-        host_out = [torch.empty((b, c, h, d), dtype=dt).pin_memory() for _ in range(4)]
+        host_in = host if backward else host[:3]
+        host_out = [torch.empty((b, c, h, d), dtype=dt).pin_memory() for _ in range(4 if backward else 1)]
         qkw = {"q_positions": pos}
         kkw = {"kv_positions": pos}
-        sm = ra.ScoreMod(causal=True)
+        if seg is not None:
+            qkw["q_segment_ids"] = seg
+            kkw["kv_segment_ids"] = seg
+        sm = ra.ScoreMod(causal=True, alibi_slopes=slopes, window=w.get("window", 0))
 
         def e2e_step():
-            dq_, dk_, dv_, ddo = (t.cuda(non_blocking=True) for t in host)
-            dq_.requires_grad_(True)
-            dk_.requires_grad_(True)
-            dv_.requires_grad_(True)
-            o = ra.ring_attention(dq_, dk_, dv_, ring, bias_fn=sm, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
+            dev = [t.cuda(non_blocking=True) for t in host_in]
+            for t in dev[:3]:
+                t.requires_grad_(backward)
+            o = ra.ring_attention(dev[0], dev[1], dev[2], ring, bias_fn=sm, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
                                   block_impl=args.block_impl)
-            o.backward(ddo)
-            for dst, src in zip(host_out, (o.detach(), dq_.grad, dk_.grad, dv_.grad)):
+            if backward:
+                o.backward(dev[3])
+            results = (o.detach(), dev[0].grad, dev[1].grad, dev[2].grad) if backward else (o.detach(),)
+            for dst, src in zip(host_out, results):
                 dst.copy_(src, non_blocking=True)
 
         for _ in range(min(args.warmup, 2)):
@@ -326,9 +387,9 @@ def main():
         t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        nbytes = sum(x.numel() * x.element_size() for x in host)
         e2e = {"value": b * w["s"] / (float(t.item()) * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": float(t.item())}
+               "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
+               "d2h_bytes_per_step": sum(x.numel() * x.element_size() for x in host_out), "ms_per_step": float(t.item())}
 
     if rank == 0:
         pk = peaks()
@@ -340,23 +401,26 @@ def main():
         fwd_flops_launch = flops(w, bwd=False) / N / N if N > 1 else flops(w, bwd=False)
         bwd_ms = sum(bwd_block_ms) / len(bwd_block_ms)
         fwd_ms = sum(fwd_block_ms) / len(fwd_block_ms)
-        achieved = bwd_flops_launch / (bwd_ms * 1e-3) / 1e12
-        peak = pk["sustained"] if bwd_ms > 5 else pk["burst"]
+        # dominant kernel: the backward block where the workload has a backward pass
+        dom_ms, dom_flops, dom_name = (bwd_ms, bwd_flops_launch, "backward") if backward else (fwd_ms, fwd_flops_launch, "forward")
+        achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+        peak = pk["sustained"] if dom_ms > 5 else pk["burst"]
+        headline = args.workload in ("causal_32k", "causal_8k") and impl_used == "tcgen05"
         line = {
-            "metric": METRIC, "value": b * w["s"] / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": N,
+            "metric": metric_name(w), "value": b * w["s"] / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": N,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "scaling": "weak" if "s_per_gpu" in w else "strong", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
             "config": workload_config(args, w, N),
             "tflops_per_gpu": tflops_gpu, "pct_bf16_peak": 100 * tflops_gpu / pk["sustained"],
             "block_impl": impl_used,
             "roofline": {
-                "bound": "tensor", "kernel": f"{impl_used} backward block", "achieved": achieved, "peak": peak,
+                "bound": "tensor", "kernel": f"{impl_used} {dom_name} block", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of this kernel from the ncu capture of the 8k-token
                 # case (profiles/tc_bwd_kernel_causal_8k.md: 3.44 GB), scaled by the visible-pair count of a launch
-                "traffic": (3.44e9 * bwd_flops_launch / 1.3746e12) if impl_used == "tcgen05" else None,
-                "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if bwd_ms > 5 else 'burst'}",
-                "launch_ms": bwd_ms, "flops_per_launch": bwd_flops_launch,
+                "traffic": (3.44e9 * bwd_flops_launch / 1.3746e12) if headline else None,
+                "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if dom_ms > 5 else 'burst'}",
+                "launch_ms": dom_ms, "flops_per_launch": dom_flops,
                 "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
             },
             "exposed_comm_ms": max(exposed_all), "exposed_comm_frac": max(exposed_all) / step_ms,

@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   const int kt = blockIdx.x / bh_count;  // K/V tile; tile 0 has the most visible queries under a causal mask
   const int hh = bh % p.h, bb = bh / p.h;
   const uint32_t kinds = p.mod.kinds;
-  const bool masked = (kinds & kMaskKinds) != 0;
+  const bool masked = (kinds & kMetaKinds) != 0;  // the tile summaries are read
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
@@ -132,76 +132,102 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 
   TileMeta mk;
   if (masked) mk = P.meta_kv[bb * P.n_kv_tiles + kt];
-  // Class of query tile i against this CTA's K/V tile: 0 skip, 1 all visible, 2 mixed.
-  auto tile_class = [&](int i) -> int {
-    if (!masked) return 1;
-    const TileMeta mq = P.meta_q[bb * P.n_q_tiles + i];
-    return classify_tiles(kinds, p.mod.window, mq, mk);
-  };
+  // First query tile >= i that has a pair visible to this CTA's K/V tile (n_q_tiles if there is
+  // none), with kMixedBit set when that tile mixes visible and masked pairs and kContigBit when
+  // its positions are contiguous.  All 32 lanes of a
+  // warp call it with the same i: each lane classifies one tile, so a long masked stretch (the
+  // tiles before the diagonal, other documents) costs one load latency per 32 tiles.
+  constexpr int kMixedBit = 1 << 16, kContigBit = 1 << 17, kTileIdx = kMixedBit - 1;
   auto next_active = [&](int i) -> int {
-    while (i < P.n_q_tiles && tile_class(i) == 0) ++i;
-    return i;
+    if (!masked) return i < P.n_q_tiles ? i : P.n_q_tiles;
+    for (; i < P.n_q_tiles; i += 32) {
+      const int t = i + lane;
+      int cls = 0;  // 0 skip, 1 all visible, 2 mixed; +4 contiguous positions
+      if (t < P.n_q_tiles) {
+        const TileMeta mq = P.meta_q[bb * P.n_q_tiles + t];
+        cls = classify_tiles(kinds, p.mod.window, mq, mk) | (mq.pos_contig ? 4 : 0);
+      }
+      const uint32_t vote = __ballot_sync(0xffffffffu, (cls & 3) != 0);
+      if (vote) {
+        const int first = __ffs(vote) - 1;
+        const int c = __shfl_sync(0xffffffffu, cls, first);
+        return (i + first) | ((c & 3) == 2 ? kMixedBit : 0) | ((c & 4) ? kContigBit : 0);
+      }
+    }
+    return P.n_q_tiles;
   };
 
   if (bad) {
     // fall through to the common exit
   } else if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
+    // The whole warp walks the tile sequence (the scan is warp-wide); lane 0 polls and issues.
     if (lane == 0) {
       prefetch_tensormap(&P.map_q);
       prefetch_tensormap(&P.map_k);
       prefetch_tensormap(&P.map_v);
       prefetch_tensormap(&P.map_do);
-      int i = next_active(0);
-      if (i < P.n_q_tiles) {
-        mbar_arrive_expect_tx(&bars[KV_FULL], 2 * TILE_BYTES);
-        for (int pn = 0; pn < PANELS; ++pn) {
-          tma_load_4d(sK + pn * PANEL_BYTES, &P.map_k, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
-          tma_load_4d(sV + pn * PANEL_BYTES, &P.map_v, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
-        }
+    }
+    const int i = next_active(0) & kTileIdx;
+    if (i < P.n_q_tiles && lane == 0) {
+      mbar_arrive_expect_tx(&bars[KV_FULL], 2 * TILE_BYTES);
+      for (int pn = 0; pn < PANELS; ++pn) {
+        tma_load_4d(sK + pn * PANEL_BYTES, &P.map_k, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
+        tma_load_4d(sV + pn * PANEL_BYTES, &P.map_v, &bars[KV_FULL], pn * 64, hh, kt * kTileRows, bb);
       }
-      // Two streams of loads: Q (with L and delta of its rows) and dO.  A Q stage is free after
-      // dK of its tile, a dO stage already after dV of its tile, one MMA group earlier in the
-      // next iteration: dO runs further ahead.  The lane polls both streams so that neither
-      // blocks the other.
-      const int64_t row_base = ((int64_t)bb * p.h + hh) * p.lq;
-      int qi = i, doi = i, qn = 0, don = 0;
-      long long t0 = 0;
-      uint32_t idle = 0;
-      while (qi < P.n_q_tiles || doi < P.n_q_tiles) {
-        bool moved = false;
-        if (qi < P.n_q_tiles && mbar_test(&bars[Q_EMPTY0 + (qn & 1)], ((qn >> 1) & 1) ^ 1)) {
+    }
+    // Two streams of loads: Q (with L and delta of its rows) and dO.  A Q stage is free after
+    // dK of its tile, a dO stage already after dV of its tile, one MMA group earlier in the
+    // next iteration: dO runs further ahead.  Both are polled so that neither blocks the other.
+    const int64_t row_base = ((int64_t)bb * p.h + hh) * p.lq;
+    int qi = i, doi = i, qn = 0, don = 0;
+    long long t0 = 0;
+    uint32_t idle = 0;
+    while (qi < P.n_q_tiles || doi < P.n_q_tiles) {
+      uint32_t ready = 0;
+      if (lane == 0) {
+        if (qi < P.n_q_tiles && mbar_test(&bars[Q_EMPTY0 + (qn & 1)], ((qn >> 1) & 1) ^ 1)) ready |= 1u;
+        if (doi < P.n_q_tiles && mbar_test(&bars[DO_EMPTY0 + (don & 1)], ((don >> 1) & 1) ^ 1)) ready |= 2u;
+      }
+      ready = __shfl_sync(0xffffffffu, ready, 0);
+      if (ready & 1u) {
+        if (lane == 0) {
           const int s = qn & 1;
           mbar_arrive_expect_tx(&bars[Q_FULL0 + s], TILE_BYTES + 2 * kTileRows * 4);
           for (int pn = 0; pn < PANELS; ++pn)
             tma_load_4d(sQ + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_q, &bars[Q_FULL0 + s], pn * 64, hh, qi * kTileRows, bb);
           bulk_load(sL + s * kTileRows, p.lse + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
           bulk_load(sDelta + s * kTileRows, p.delta + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
-          qi = next_active(qi + 1);
-          ++qn;
-          moved = true;
         }
-        if (doi < P.n_q_tiles && mbar_test(&bars[DO_EMPTY0 + (don & 1)], ((don >> 1) & 1) ^ 1)) {
+        qi = next_active(qi + 1) & kTileIdx;
+        ++qn;
+      }
+      if (ready & 2u) {
+        if (lane == 0) {
           const int s = don & 1;
           mbar_arrive_expect_tx(&bars[DO_FULL0 + s], TILE_BYTES);
           for (int pn = 0; pn < PANELS; ++pn)
             tma_load_4d(sdO + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_do, &bars[DO_FULL0 + s], pn * 64, hh, doi * kTileRows, bb);
-          doi = next_active(doi + 1);
-          ++don;
-          moved = true;
         }
-        if (moved) {
-          t0 = 0;
-        } else if ((++idle & 63u) == 0) {  // bounded polling
-          if (*abort_flag) break;
+        doi = next_active(doi + 1) & kTileIdx;
+        ++don;
+      }
+      if (ready) {
+        t0 = 0;
+      } else if ((++idle & 63u) == 0) {  // bounded polling
+        uint32_t stop = 0;
+        if (lane == 0) {
           const long long now = clock64();
           if (t0 == 0) t0 = now;
-          if (now - t0 > kWaitCycles) {
+          if (*abort_flag) {
+            stop = 1;
+          } else if (now - t0 > kWaitCycles) {
             *abort_flag = 1;
             atomicOr(P.status, kStBwdProducer);
-            break;
+            stop = 1;
           }
         }
+        if (__shfl_sync(0xffffffffu, stop, 0)) break;
       }
     }
   } else if (warp == 9) {
@@ -258,7 +284,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 #define PROF_BEGIN() do {} while (0)
 #define PROF_END(slot) do {} while (0)
 #endif
-      int i = __shfl_sync(0xffffffffu, next_active(0), 0);
+      int i = next_active(0) & kTileIdx;
       if (i < P.n_q_tiles) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
                                          mbar_wait(&bars[Q_FULL0], 0, abort_flag, P.status, kStBwdMma) &&
@@ -277,7 +303,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         for (int n = 0; ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
           const uint32_t par = n & 1;
-          const int inext = __shfl_sync(0xffffffffu, next_active(i + 1), 0);
+          const int inext = next_active(i + 1) & kTileIdx;
           const bool has_next = inext < P.n_q_tiles;
           TRACE(0, 1);
           if (has_next) {
@@ -373,29 +399,38 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     if (p.mod.kv_seg) kseg = p.mod.kv_seg[(int64_t)bb * p.lk + kv_row];
     if (p.mod.kv_pre) kpre = p.mod.kv_pre[(int64_t)bb * p.lk + kv_row] != 0;
     const int64_t qrow_base = ((int64_t)bb * p.h + hh) * p.lq;
-    bool ok = true;
+    bool ok = true;  // warp-uniform: the tile scan below votes across the warp
     float pf[64];        // P^T of the tile whose dS^T is formed next (this thread's row, 64 columns)
     uint32_t sv[2][32];
     const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
+    const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
+    // first query position of a tile (ALiBi only), read one tile ahead like the tile class
+    auto first_qpos = [&](int e) -> int32_t {
+      return (alibi && (e & kTileIdx) < P.n_q_tiles) ? p.mod.q_pos[(int64_t)bb * p.lq + (int64_t)(e & kTileIdx) * kTileRows] : 0;
+    };
 
     // One loop body serves every tile so that each phase exists once in the instruction
     // stream: step k does dS^T(k-1), then P^T(k), then the dQ drain of tile k-1.
-    int i_prev = -1, i_cur = next_active(0);
+    int i_prev = -1, e_cur = next_active(0), i_cur = e_cur & kTileIdx;
+    int32_t q0_cur = first_qpos(e_cur);
     for (int k = 0; ok; ++k) {
       const bool have_prev = k > 0, have_cur = i_cur < P.n_q_tiles;
       if (!have_prev && !have_cur) break;
+      // looked up here so that the load's latency passes under the work below
+      const int e_next = have_cur ? next_active(i_cur + 1) : P.n_q_tiles;
+      const int32_t q0_next = first_qpos(e_next);
       if (have_prev) {
         // ---- dS^T = P^T * (dP^T - delta) of tile k-1 -> shared memory, 128-byte swizzle
         const int n = k - 1, s = n & 1;
         const float4* Dls = reinterpret_cast<const float4*>(sDelta + s * kTileRows + g * 64);
         if (threadIdx.x == 0) TRACE(1, 10);
-        if (!(ok = mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
         if (threadIdx.x == 0) TRACE(1, 11);
         tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
         tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
         tc_wait_ld();
-        if (!(ok = mbar_wait(&bars[DS_FREE], (n & 1) ^ 1, abort_flag, P.status, kStBwdCompute))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_FREE], (n & 1) ^ 1, abort_flag, P.status, kStBwdCompute)))) break;
         uint8_t* row_ptr = sdS + g * PANEL_BYTES + r * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
@@ -419,13 +454,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       if (have_cur) {
         // ---- P^T = exp2(S^T * scale2 - L * log2e) of tile k on this warpgroup's 64 query columns
         const int n = k, s = n & 1, i = i_cur;
-        const bool need_mask = masked && tile_class(i) == 2;
-        if (!(ok = mbar_wait(&bars[Q_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute))) break;
+        const bool need_mask = (e_cur & kMixedBit) != 0;
+        // ALiBi over a tile of contiguous query positions with nothing masked is two FMAs per
+        // score in registers; every other ALiBi tile takes the in-TMEM pass below
+        const bool alibi_inline = alibi && !need_mask && (e_cur & kContigBit) != 0;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL0 + s], (n >> 1) & 1, abort_flag, P.status, kStBwdCompute)))) break;
         const float4* Ls = reinterpret_cast<const float4*>(sL + s * kTileRows + g * 64);
-        if (!(ok = mbar_wait(&bars[S_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[S_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
         if (threadIdx.x == 0) TRACE(1, 13);
-        if (need_mask || alibi) {  // rare: tiles that mix visible and masked pairs, or ALiBi
+        if (need_mask || (alibi && !alibi_inline)) {  // tiles that mix visible and masked pairs, ALiBi over scattered positions
           const int64_t q0 = (int64_t)bb * p.lq + (int64_t)i * kTileRows + g * 64;
           fixup_scores_tmem<false>(tmem_S + lane_off + g * 64, 64, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
                                    p.mod.window, alibi_over_scale, kpos, kseg, kpre,
@@ -435,6 +473,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         tmem_ld32(tmem_S + lane_off + g * 64, sv[0]);
         tmem_ld32(tmem_S + lane_off + g * 64 + 32, sv[1]);
         tc_wait_ld();
+        float sc = scale2;  // what is left to multiply the register values by
+        if (alibi_inline) {
+          // scale * s - slope * (q_pos - kv_pos), times log2(e), with q_pos = q0 + column; the
+          // position differences are exact in fp32
+          const float rr = slope2 * (float)(kpos - (q0_cur + g * 64));
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            sv[c >> 5][c & 31] = __float_as_uint(fmaf(-slope2, (float)c, fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, rr)));
+          sc = 1.f;
+        }
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 lv = Ls[c4];
@@ -445,7 +493,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
             // a masked pair (-inf) gives exp2(-inf) = 0; the clamp keeps a row whose L is -inf
             // (it saw no key) from turning that into exp2(-inf + inf)
             const float neg_l2 = fminf(-l4[e] * kLog2e, 1e30f);
-            pf[c] = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, neg_l2));
+            pf[c] = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, neg_l2));
           }
         }
         uint32_t pk[32];
@@ -460,7 +508,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       if (have_prev) {
         // ---- dQ of tile k-1: rows are queries; add this warpgroup's half of the columns
         const int n = k - 1;
-        if (!(ok = mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
         if (threadIdx.x == 0) TRACE(1, 15);
         if constexpr (D == 128) {
@@ -492,7 +540,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       }
       if (!have_cur) break;
       i_prev = i_cur;
-      i_cur = next_active(i_cur + 1);
+      e_cur = e_next;
+      i_cur = e_cur & kTileIdx;
+      q0_cur = q0_next;
     }
     const int n = (i_prev >= 0) ? 1 : 0;  // whether this CTA had any tile
     // ---- epilogue: dK, dV of this K/V tile
@@ -630,7 +680,7 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
   if (!P.status) return cudaErrorInvalidSymbol;
   TileMeta* meta = nullptr;
   cudaError_t e;
-  if (p.mod.kinds & kMaskKinds) {
+  if (p.mod.kinds & kMetaKinds) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
     if ((e = cudaMallocAsync((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
     TileMeta* mq = meta;

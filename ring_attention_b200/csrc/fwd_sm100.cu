@@ -87,10 +87,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
   }
   if (warp == 0) {
     // List of K/V tiles this CTA visits: index in bits 0-11, "query tile t needs mask
-    // arithmetic on it" in bit 12+t.  Tiles masked for both query tiles are left out.
+    // arithmetic on it" in bit 12+t, "the tile's positions are contiguous" in bit 14.  Tiles
+    // masked for both query tiles are left out.
     int cnt = 0;
     TileMeta mq0, mq1;
-    const bool masked = (kinds & kMaskKinds) != 0;
+    const bool masked = (kinds & kMetaKinds) != 0;
     if (masked) {
       mq0 = P.meta_q[bb * P.n_q_tiles + qt0];
       mq1 = P.meta_q[bb * P.n_q_tiles + qt0 + (ntile - 1)];
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         const int c0 = classify_tiles(kinds, p.mod.window, mq0, mk);
         const int c1 = ntile == 2 ? classify_tiles(kinds, p.mod.window, mq1, mk) : 0;
         active = (c0 != 0) || (c1 != 0);
-        code = (c0 != 1 ? 1u : 0u) | (c1 != 1 ? 2u : 0u);
+        code = (c0 != 1 ? 1u : 0u) | (c1 != 1 ? 2u : 0u) | (mk.pos_contig ? 4u : 0u);
       }
       const uint32_t vote = __ballot_sync(0xffffffffu, active);
       if (active) list[cnt + __popc(vote & ((1u << lane) - 1))] = (uint16_t)(j | (code << 12));
@@ -224,12 +225,20 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
     bool ok = true;
 
     const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
+    const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
+    // first position of the K/V tile the loop is about to visit (ALiBi only), read one tile ahead
+    int32_t k0_next = (alibi && count > 0) ? p.mod.kv_pos[(int64_t)bb * p.lk + (int64_t)(list[0] & 0xFFF) * kTileRows] : 0;
     for (int i = 0; i < count; ++i) {
       const int j = list[i] & 0xFFF;
       const bool need_mask = ((list[i] >> (12 + t)) & 1) != 0;
+      // ALiBi over a tile of contiguous key positions with nothing masked is two FMAs per score
+      // in registers; every other ALiBi tile takes the in-TMEM pass below
+      const bool alibi_inline = alibi && !need_mask && ((list[i] >> 14) & 1) != 0;
+      const int32_t k0 = k0_next;
+      if (alibi && i + 1 < count) k0_next = p.mod.kv_pos[(int64_t)bb * p.lk + (int64_t)(list[i + 1] & 0xFFF) * kTileRows];
       if (!(ok = mbar_wait(&bars[S_FULL0 + t], i & 1, abort_flag, P.status, kStFwdSoftmax))) break;
       tc_fence_after();
-      if (need_mask || alibi) {  // rare: tiles that mix visible and masked pairs, or ALiBi
+      if (need_mask || (alibi && !alibi_inline)) {  // tiles that mix visible and masked pairs, ALiBi over scattered positions
         const int64_t kv0 = (int64_t)bb * p.lk + (int64_t)j * kTileRows;
         fixup_scores_tmem<true>(tmem_S[t] + lane_off, kTileRows, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
                                 p.mod.window, alibi_over_scale, qpos, qseg, qpre,
@@ -240,12 +249,25 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[t] + lane_off + c * 32, r[c]);
       tc_wait_ld();
+      // sc: what is left to multiply the register values by (the ALiBi form has the scale in already)
+      float sc = scale2;
+      if (alibi_inline) {
+        // scale * s - slope * (q_pos - kv_pos), times log2(e): the bias of ring_test.py-style ALiBi
+        // callables, with kv_pos = k0 + column; the differences are exact in fp32
+        const float r_i = slope2 * (float)(k0 - qpos);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            r[c][e] = __float_as_uint(fmaf(slope2, (float)(c * 32 + e), fmaf(__uint_as_float(r[c][e]), scale2, r_i)));
+        sc = 1.f;
+      }
       float mx = -INFINITY;  // raw scores; the scale is positive, so it commutes with max
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[c][e]));
-      const float m_new = fmaxf(m_true, mx * scale2);
+      const float m_new = fmaxf(m_true, mx * sc);
       m_true = m_new;
       const bool need = (m_new > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
       if (__any_sync(0xffffffffu, need)) {
@@ -272,8 +294,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(r[c][2 * e]), scale2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(r[c][2 * e + 1]), scale2, neg_m));
+          const float p0 = ex2(fmaf(__uint_as_float(r[c][2 * e]), sc, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(r[c][2 * e + 1]), sc, neg_m));
           sum += p0 + p1;
           pk[e] = pack_bf16(p0, p1);
         }
@@ -358,12 +380,14 @@ __global__ void tile_meta_kernel(TileMeta* __restrict__ out, const int32_t* __re
   const int lane = threadIdx.x & 31, bb = blockIdx.y;
   if (tile >= n_tiles) return;
   const int64_t base = (int64_t)bb * len + (int64_t)tile * kTileRows;
-  int pmin = INT32_MAX, pmax = INT32_MIN, smin = INT32_MAX, smax = INT32_MIN, any = 0, all = 1;
+  int pmin = INT32_MAX, pmax = INT32_MIN, smin = INT32_MAX, smax = INT32_MIN, any = 0, all = 1, contig = 1;
+  const int p0 = pos ? pos[base] : 0;
   for (int e = lane; e < kTileRows; e += 32) {
     if (pos) {
       int v = pos[base + e];
       pmin = min(pmin, v);
       pmax = max(pmax, v);
+      contig &= (v == p0 + e) ? 1 : 0;
     }
     if (seg) {
       int v = seg[base + e];
@@ -384,6 +408,7 @@ __global__ void tile_meta_kernel(TileMeta* __restrict__ out, const int32_t* __re
     smax = max(smax, __shfl_xor_sync(0xffffffffu, smax, o));
     any |= __shfl_xor_sync(0xffffffffu, any, o);
     all &= __shfl_xor_sync(0xffffffffu, all, o);
+    contig &= __shfl_xor_sync(0xffffffffu, contig, o);
   }
   if (lane == 0) {
     TileMeta m;
@@ -393,7 +418,8 @@ __global__ void tile_meta_kernel(TileMeta* __restrict__ out, const int32_t* __re
     m.seg_max = seg ? smax : 0;
     m.pre_any = pre ? any : 0;
     m.pre_all = pre ? all : 0;
-    m.pad0 = m.pad1 = 0;
+    m.pos_contig = pos ? contig : 0;
+    m.pad1 = 0;
     out[(int64_t)bb * n_tiles + tile] = m;
   }
 }
@@ -502,7 +528,7 @@ cudaError_t tc_fwd_block(const FwdParams& p, cudaStream_t s) {
   if (!P.status) return cudaErrorInvalidSymbol;
   TileMeta* meta = nullptr;
   cudaError_t e;
-  if (p.mod.kinds & kMaskKinds) {
+  if (p.mod.kinds & kMetaKinds) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
     if ((e = cudaMallocAsync((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
     TileMeta* mq = meta;
@@ -614,7 +640,7 @@ extern "C" int ra_fwd_block_static(const ra_shape_t* shape, const ra_tensor_t* q
   if (!P.status) return fail(RA_ERR_CUDA, "status word symbol not found");
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
-  if (p.mod.kinds & kMaskKinds) {
+  if (p.mod.kinds & kMetaKinds) {
     TileMeta* meta = nullptr;
     if ((e = static_tile_meta(&meta)) != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
     TileMeta* mq = meta;

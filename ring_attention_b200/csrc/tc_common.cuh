@@ -14,7 +14,9 @@ constexpr int kMaxTiles = 4096;    // most tiles one block (shard) may have alon
 // Range summary of the per-token score-mod arrays over one 128-token tile.
 struct TileMeta {
   int32_t pos_min, pos_max, seg_min, seg_max;
-  int32_t pre_any, pre_all, pad0, pad1;
+  int32_t pre_any, pre_all;
+  int32_t pos_contig;  // 1 when the tile's positions are pos[0], pos[0] + 1, ... (then pos[0] == pos_min)
+  int32_t pad1;
 };
 
 // 0: every pair of the tile pair is masked; 1: every pair is visible; 2: mixed.
@@ -42,6 +44,8 @@ __device__ __forceinline__ int classify_tiles(uint32_t kinds, int32_t window, co
 }
 
 constexpr uint32_t kMaskKinds = RA_MOD_CAUSAL | RA_MOD_SEGMENT | RA_MOD_PREFIX | RA_MOD_WINDOW;
+// Score-mods that read the tile summaries (ALiBi reads pos_contig to choose its in-loop form).
+constexpr uint32_t kMetaKinds = kMaskKinds | RA_MOD_ALIBI;
 
 // Applies the score-mod to raw (unscaled) scores that sit in TMEM, in place: this thread's
 // TMEM lane, `ncols` columns from `taddr`.  Masked pairs become -inf and the ALiBi bias is

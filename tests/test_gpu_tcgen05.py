@@ -62,7 +62,7 @@ def test_fwd_block_state(b, h, lq, lk, d):
 
 MODS = [
     dict(causal=True), dict(causal=True, seg=True), dict(seg=True), dict(seg=True, prefix=True),
-    dict(prefix=True), dict(causal=True, alibi=True), dict(causal=True, alibi=True, window=300),
+    dict(prefix=True), dict(causal=True, alibi=True), dict(causal=True, alibi=True, window=300), dict(alibi=True),
     dict(causal=True, window=200), dict(window=256),
 ]
 
