@@ -315,6 +315,9 @@ def main():
     e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     flush_ms = 0.0
     with ClockSampler(local) as clocks:
+        # the device idled while the sampler started (its clocks may have dropped): one more
+        # untimed step right before the timed region
+        step()
         barrier()
         # K steps back to back with no host synchronisation in between; the device clock brackets them
         e_begin.record()

@@ -404,9 +404,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     uint32_t sv[2][32];
     const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
     const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
-    // first query position of a tile (ALiBi only), read one tile ahead like the tile class
+    // first query position of a tile, read one tile ahead like the tile class
     auto first_qpos = [&](int e) -> int32_t {
-      return (alibi && (e & kTileIdx) < P.n_q_tiles) ? p.mod.q_pos[(int64_t)bb * p.lq + (int64_t)(e & kTileIdx) * kTileRows] : 0;
+      return (p.mod.q_pos && (e & kTileIdx) < P.n_q_tiles) ? p.mod.q_pos[(int64_t)bb * p.lq + (int64_t)(e & kTileIdx) * kTileRows] : 0;
     };
 
     // One loop body serves every tile so that each phase exists once in the instruction
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           fixup_scores_tmem<false>(tmem_S + lane_off + g * 64, 64, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
                                    p.mod.window, alibi_over_scale, kpos, kseg, kpre,
                                    p.mod.q_pos ? p.mod.q_pos + q0 : nullptr, p.mod.q_seg ? p.mod.q_seg + q0 : nullptr,
-                                   p.mod.q_pre ? p.mod.q_pre + q0 : nullptr);
+                                   p.mod.q_pre ? p.mod.q_pre + q0 : nullptr, q0_cur + g * 64, (e_cur & kContigBit) != 0);
         }
         tmem_ld32(tmem_S + lane_off + g * 64, sv[0]);
         tmem_ld32(tmem_S + lane_off + g * 64 + 32, sv[1]);

@@ -56,7 +56,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
   uint8_t* sK = sQ + 2 * TILE_BYTES;
   uint8_t* sV = sK + 2 * TILE_BYTES;
   uint16_t* list = reinterpret_cast<uint16_t*>(sV + 2 * TILE_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(list + kMaxTiles);
+  uint8_t* codes = reinterpret_cast<uint8_t*>(list + kMaxTiles);  // [kMaxTiles] class of each K/V tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(codes + kMaxTiles);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* count_slot = reinterpret_cast<int*>(tmem_slot + 2);
@@ -85,27 +86,32 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 0) {
-    // List of K/V tiles this CTA visits: index in bits 0-11, "query tile t needs mask
-    // arithmetic on it" in bit 12+t, "the tile's positions are contiguous" in bit 14.  Tiles
-    // masked for both query tiles are left out.
-    int cnt = 0;
-    TileMeta mq0, mq1;
-    const bool masked = (kinds & kMetaKinds) != 0;
-    if (masked) {
-      mq0 = P.meta_q[bb * P.n_q_tiles + qt0];
-      mq1 = P.meta_q[bb * P.n_q_tiles + qt0 + (ntile - 1)];
+  // List of K/V tiles this CTA visits: index in bits 0-11, "query tile t needs mask arithmetic
+  // on it" in bit 12+t, "the tile's positions are contiguous" in bit 14.  Tiles masked for both
+  // query tiles are left out.  Every thread classifies its share of the tiles (one round of
+  // loads for up to 320 tiles), then warp 0 compacts the classes in order.
+  const bool masked = (kinds & kMetaKinds) != 0;
+  if (masked) {
+    const TileMeta mq0 = P.meta_q[bb * P.n_q_tiles + qt0];
+    const TileMeta mq1 = P.meta_q[bb * P.n_q_tiles + qt0 + (ntile - 1)];
+    for (int j = threadIdx.x; j < P.n_kv_tiles; j += blockDim.x) {
+      const TileMeta mk = P.meta_kv[bb * P.n_kv_tiles + j];
+      const int c0 = classify_tiles(kinds, p.mod.window, mq0, mk);
+      const int c1 = ntile == 2 ? classify_tiles(kinds, p.mod.window, mq1, mk) : 0;
+      const uint32_t code = (c0 != 1 ? 1u : 0u) | (c1 != 1 ? 2u : 0u) | (mk.pos_contig ? 4u : 0u);
+      codes[j] = ((c0 != 0) || (c1 != 0)) ? (uint8_t)(0x80u | code) : (uint8_t)0;  // bit 7: visited
     }
+    __syncthreads();
+  }
+  if (warp == 0) {
+    int cnt = 0;
     for (int base = 0; base < P.n_kv_tiles; base += 32) {
       const int j = base + lane;
-      uint32_t code = 0;
       bool active = j < P.n_kv_tiles;
+      uint32_t code = 0;
       if (active && masked) {
-        const TileMeta mk = P.meta_kv[bb * P.n_kv_tiles + j];
-        const int c0 = classify_tiles(kinds, p.mod.window, mq0, mk);
-        const int c1 = ntile == 2 ? classify_tiles(kinds, p.mod.window, mq1, mk) : 0;
-        active = (c0 != 0) || (c1 != 0);
-        code = (c0 != 1 ? 1u : 0u) | (c1 != 1 ? 2u : 0u) | (mk.pos_contig ? 4u : 0u);
+        code = codes[j] & 0x7u;
+        active = (codes[j] & 0x80u) != 0;
       }
       const uint32_t vote = __ballot_sync(0xffffffffu, active);
       if (active) list[cnt + __popc(vote & ((1u << lane) - 1))] = (uint16_t)(j | (code << 12));
@@ -226,16 +232,18 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
 
     const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
     const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
-    // first position of the K/V tile the loop is about to visit (ALiBi only), read one tile ahead
-    int32_t k0_next = (alibi && count > 0) ? p.mod.kv_pos[(int64_t)bb * p.lk + (int64_t)(list[0] & 0xFFF) * kTileRows] : 0;
+    // first position of the K/V tile the loop is about to visit, read one tile ahead
+    const bool has_pos = p.mod.kv_pos != nullptr;
+    int32_t k0_next = (has_pos && count > 0) ? p.mod.kv_pos[(int64_t)bb * p.lk + (int64_t)(list[0] & 0xFFF) * kTileRows] : 0;
     for (int i = 0; i < count; ++i) {
       const int j = list[i] & 0xFFF;
       const bool need_mask = ((list[i] >> (12 + t)) & 1) != 0;
       // ALiBi over a tile of contiguous key positions with nothing masked is two FMAs per score
       // in registers; every other ALiBi tile takes the in-TMEM pass below
-      const bool alibi_inline = alibi && !need_mask && ((list[i] >> 14) & 1) != 0;
+      const bool kv_contig = ((list[i] >> 14) & 1) != 0;
+      const bool alibi_inline = alibi && !need_mask && kv_contig;
       const int32_t k0 = k0_next;
-      if (alibi && i + 1 < count) k0_next = p.mod.kv_pos[(int64_t)bb * p.lk + (int64_t)(list[i + 1] & 0xFFF) * kTileRows];
+      if (has_pos && i + 1 < count) k0_next = p.mod.kv_pos[(int64_t)bb * p.lk + (int64_t)(list[i + 1] & 0xFFF) * kTileRows];
       if (!(ok = mbar_wait(&bars[S_FULL0 + t], i & 1, abort_flag, P.status, kStFwdSoftmax))) break;
       tc_fence_after();
       if (need_mask || (alibi && !alibi_inline)) {  // tiles that mix visible and masked pairs, ALiBi over scattered positions
@@ -243,7 +251,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         fixup_scores_tmem<true>(tmem_S[t] + lane_off, kTileRows, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
                                 p.mod.window, alibi_over_scale, qpos, qseg, qpre,
                                 p.mod.kv_pos ? p.mod.kv_pos + kv0 : nullptr, p.mod.kv_seg ? p.mod.kv_seg + kv0 : nullptr,
-                                p.mod.kv_pre ? p.mod.kv_pre + kv0 : nullptr);
+                                p.mod.kv_pre ? p.mod.kv_pre + kv0 : nullptr, k0, kv_contig);
       }
       uint32_t r[4][32];
 #pragma unroll
@@ -446,7 +454,7 @@ EncodeTiledFn encode_fn() {
 
 template <int D>
 cudaError_t launch_fwd(const FwdTcParams& P, cudaStream_t s) {
-  constexpr size_t kSmem = 6 * kTileRows * D * 2 + kMaxTiles * 2 + NUM_BARS * 8 + 64 + 1024;
+  constexpr size_t kSmem = 6 * kTileRows * D * 2 + kMaxTiles * 3 + NUM_BARS * 8 + 64 + 1024;
   constexpr size_t kRequest = kSmem < 120 * 1024 ? 120 * 1024 : kSmem;  // one CTA per SM: it owns all of TMEM
   auto kern = tc_fwd_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRequest);

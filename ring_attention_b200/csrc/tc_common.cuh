@@ -48,35 +48,44 @@ constexpr uint32_t kMaskKinds = RA_MOD_CAUSAL | RA_MOD_SEGMENT | RA_MOD_PREFIX |
 constexpr uint32_t kMetaKinds = kMaskKinds | RA_MOD_ALIBI;
 
 // Applies the score-mod to raw (unscaled) scores that sit in TMEM, in place: this thread's
-// TMEM lane, `ncols` columns from `taddr`.  Masked pairs become -inf and the ALiBi bias is
-// added divided by the softmax scale, so that the kernels' main loops, which multiply by
-// the scale, see exactly scale * s + bias.  Only tiles that mix visible and masked pairs
-// (or any tile under ALiBi) come here; it is a rolled loop on purpose: the main loops stay
-// free of mask code and small enough for the instruction cache.
+// TMEM lane, `ncols` columns (a multiple of 16) from `taddr`.  Masked pairs become -inf and the
+// ALiBi bias is added divided by the softmax scale, so that the kernels' main loops, which
+// multiply by the scale, see exactly scale * s + bias.  Only tiles that mix visible and masked
+// pairs (or ALiBi tiles over scattered positions) come here; it is a rolled loop on purpose: the
+// main loops stay free of mask code and small enough for the instruction cache.  The next 16
+// columns are in flight while the current 16 are worked on.  When the columns' positions are
+// contiguous (`col_contig`: position of column c is col_pos0 + c) they are not loaded.
 // kRowIsQuery: the thread's row is a query and columns are keys (forward); else the thread's
 // row is a key and columns are queries (backward, transposed tiles).
 template <bool kRowIsQuery>
 __device__ __noinline__ void fixup_scores_tmem(uint32_t taddr, int ncols, uint32_t kinds, int32_t window,
                                                float alibi_over_scale, int32_t row_pos, int32_t row_seg,
                                                bool row_pre, const int32_t* col_pos, const int32_t* col_seg,
-                                               const uint8_t* col_pre) {
+                                               const uint8_t* col_pre, int32_t col_pos0, bool col_contig) {
+  uint32_t cur[16], nxt[16];
+  ptx::tmem_ld16(taddr, cur);
 #pragma unroll 1
-  for (int c0 = 0; c0 < ncols; c0 += 8) {
-    uint32_t r[8];
-    ptx::tmem_ld8(taddr + c0, r);
+  for (int c0 = 0; c0 < ncols; c0 += 16) {
     ptx::tc_wait_ld();
+    const bool more = c0 + 16 < ncols;
+    if (more) ptx::tmem_ld16(taddr + c0 + 16, nxt);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int32_t cpos = col_pos ? __ldg(col_pos + c0 + e) : 0;
+    for (int e = 0; e < 16; ++e) {
+      const int32_t cpos = col_contig ? col_pos0 + c0 + e : (col_pos ? __ldg(col_pos + c0 + e) : 0);
       const int32_t cseg = col_seg ? __ldg(col_seg + c0 + e) : 0;
       const bool cpre = col_pre ? (__ldg(col_pre + c0 + e) != 0) : false;
-      const float x = __uint_as_float(r[e]);
+      const float x = __uint_as_float(cur[e]);
       const float y = kRowIsQuery
                           ? apply_mod(x, kinds, window, alibi_over_scale, row_pos, row_seg, row_pre, cpos, cseg, cpre)
                           : apply_mod(x, kinds, window, alibi_over_scale, cpos, cseg, cpre, row_pos, row_seg, row_pre);
-      r[e] = __float_as_uint(y);
+      cur[e] = __float_as_uint(y);
     }
-    ptx::tmem_st8(taddr + c0, r);
+    ptx::tmem_st16(taddr + c0, cur);
+    if (more) {
+      ptx::tc_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) cur[e] = nxt[e];
+    }
   }
   ptx::tc_wait_st();
 }
