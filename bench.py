@@ -336,10 +336,9 @@ def main():
         torch.cuda.synchronize()
         flush_ms = f0.elapsed_time(f1) / args.steps
     # device times of the last step's block kernels and transfer waits (events recorded inside the timed region)
-    ms, n = ring.last_block_ms(False)
-    fwd_block_ms = [ms / max(n, 1)]
-    ms, n = ring.last_block_ms(True) if backward else (0.0, 1)
-    bwd_block_ms = [ms / max(n, 1)]
+    # (total device time of this rank's block launches in the last step, number of launches)
+    fwd_blocks = ring.last_block_ms(False)
+    bwd_blocks = ring.last_block_ms(True) if backward else (0.0, 1)
     exposed_ms = [ring.last_timing(False)[1] + (ring.last_timing(True)[1] if backward else 0.0)]
     launches = lib.ra_launch_count() - launches0
     step_ms = e_begin.elapsed_time(e_end) / args.steps - flush_ms
@@ -398,12 +397,13 @@ def main():
         pk = peaks()
         total_flops = flops(w)
         tflops_gpu = total_flops / N / (step_ms * 1e-3) / 1e12
-        # dominant kernel: the backward block kernel.  Algorithmic FLOPs of one launch: the
-        # visible pairs of one (q shard, kv block) pair; averaged over the ring's steps.
-        bwd_flops_launch = flops(w, fwd=False) / N / N if N > 1 else flops(w, fwd=False)
-        fwd_flops_launch = flops(w, bwd=False) / N / N if N > 1 else flops(w, bwd=False)
-        bwd_ms = sum(bwd_block_ms) / len(bwd_block_ms)
-        fwd_ms = sum(fwd_block_ms) / len(fwd_block_ms)
+        # dominant kernel: the backward block kernel.  Algorithmic FLOPs of one launch: this rank's
+        # share of the visible pairs, averaged over its block launches of one step (N forward
+        # launches; N, or N + 1 with the own block in two parts, backward launches).
+        bwd_flops_launch = flops(w, fwd=False) / N / max(bwd_blocks[1], 1)
+        fwd_flops_launch = flops(w, bwd=False) / N / max(fwd_blocks[1], 1)
+        bwd_ms = bwd_blocks[0] / max(bwd_blocks[1], 1)
+        fwd_ms = fwd_blocks[0] / max(fwd_blocks[1], 1)
         # dominant kernel: the backward block where the workload has a backward pass
         dom_ms, dom_flops, dom_name = (bwd_ms, bwd_flops_launch, "backward") if backward else (fwd_ms, fwd_flops_launch, "forward")
         achieved = dom_flops / (dom_ms * 1e-3) / 1e12
@@ -424,6 +424,7 @@ def main():
                 "traffic": (3.44e9 * bwd_flops_launch / 1.3746e12) if headline else None,
                 "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if dom_ms > 5 else 'burst'}",
                 "launch_ms": dom_ms, "flops_per_launch": dom_flops,
+                "launches_per_step": int(bwd_blocks[1] if backward else fwd_blocks[1]),
                 "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
             },
             "exposed_comm_ms": max(exposed_all), "exposed_comm_frac": max(exposed_all) / step_ms,

@@ -720,6 +720,39 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   return end_call(ring, 0, stream);
 }
 
+namespace ringimpl {
+// The part of a backward block call that covers batch elements [b0, b0 + nb) and heads
+// [h0, h0 + nh) (a head range only with one batch element: the fp32 state arrays are
+// [b, h, len, d] and must stay dense).  Everything is a pointer offset; shapes shrink.
+BwdParams sub_problem(const BwdParams& p, int esize, int b0, int nb, int h0, int nh) {
+  BwdParams s = p;
+  auto view = [&](TensorView t) {
+    if (t.ptr) t.ptr = (const char*)t.ptr + ((int64_t)b0 * t.sb + (int64_t)h0 * t.sh) * esize;
+    return t;
+  };
+  s.q = view(p.q);
+  s.k = view(p.k);
+  s.v = view(p.v);
+  s.dout = view(p.dout);
+  if (s.mod.q_pos) s.mod.q_pos += (int64_t)b0 * p.lq;
+  if (s.mod.q_seg) s.mod.q_seg += (int64_t)b0 * p.lq;
+  if (s.mod.q_pre) s.mod.q_pre += (int64_t)b0 * p.lq;
+  if (s.mod.kv_pos) s.mod.kv_pos += (int64_t)b0 * p.lk;
+  if (s.mod.kv_seg) s.mod.kv_seg += (int64_t)b0 * p.lk;
+  if (s.mod.kv_pre) s.mod.kv_pre += (int64_t)b0 * p.lk;
+  if (s.mod.slopes) s.mod.slopes += h0;
+  const int64_t bh0 = (int64_t)b0 * p.h + h0;
+  s.lse = p.lse + bh0 * p.lq;
+  s.delta = p.delta + bh0 * p.lq;
+  s.dq = p.dq + bh0 * p.lq * p.dk_dim;
+  s.dk = p.dk + bh0 * p.lk * p.dk_dim;
+  s.dv = p.dv + bh0 * p.lk * p.dv_dim;
+  s.b = nb;
+  s.h = nh;
+  return s;
+}
+}  // namespace ringimpl
+
 int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
                 const ra_tensor_t* k, const ra_tensor_t* v, const ra_tensor_t* out,
                 const float* lse, const ra_tensor_t* dout, const ra_score_mod_t* mod,
@@ -758,12 +791,33 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   const size_t krows = (size_t)shape->b * shape->h * shape->lk;
   const size_t delta_b = align_up(qrows * 4), dq_b = align_up(qrows * shape->dk * 4);
   const size_t dk_b = align_up(krows * shape->dk * 4), dv_b = align_up(krows * shape->dv * 4);
-  RA_CUDA(ring->grads.reserve(delta_b + dq_b + dk_b + dv_b), "cudaMalloc(grads)");
+  // With more than one rank the own block is computed in two parts, the first before and the
+  // second after the remote blocks: the second part runs while the last remote block's dK/dV
+  // contributions are still travelling and being summed, which would otherwise be exposed.
+  // The parts are batch halves, or head halves when there is one batch element; the second
+  // part's dK/dV go to a buffer of their own (the owner-side sums write the accumulators
+  // meanwhile) and are added at the end.
+  const int N_ = ring->nranks;
+  const int esize = shape->dtype == RA_DTYPE_BF16 ? 2 : 4;
+  bool split_b = N_ > 1 && shape->b >= 2, split_h = N_ > 1 && shape->b == 1 && shape->h >= 2;
+  {
+    // the final sum of the second part reads float4: its first row must sit on a 16-byte boundary
+    const int64_t off = ((int64_t)(split_b ? shape->b / 2 : 0) * shape->h + (split_h ? shape->h / 2 : 0)) * shape->lk;
+    if ((off * shape->dk) % 4 || (off * shape->dv) % 4) split_b = split_h = false;
+  }
+  const bool split = split_b || split_h;
+  const int b0 = split_b ? shape->b / 2 : 0, h0 = split_h ? shape->h / 2 : 0;
+  const int nb2 = split_b ? shape->b - b0 : shape->b, nh2 = split_h ? shape->h - h0 : shape->h;
+  const size_t rows2 = split ? (size_t)nb2 * nh2 * shape->lk : 0;
+  const size_t own2_dk_b = align_up(rows2 * shape->dk * 4), own2_dv_b = align_up(rows2 * shape->dv * 4);
+  RA_CUDA(ring->grads.reserve(delta_b + dq_b + dk_b + dv_b + own2_dk_b + own2_dv_b), "cudaMalloc(grads)");
   char* g = (char*)ring->grads.ptr;
   float* delta = (float*)g;
   float* dq_acc = (float*)(g + delta_b);
   float* dk_acc = (float*)(g + delta_b + dq_b);
   float* dv_acc = (float*)(g + delta_b + dq_b + dk_b);
+  float* own2_dk = (float*)(g + delta_b + dq_b + dk_b + dv_b);
+  float* own2_dv = (float*)(g + delta_b + dq_b + dk_b + dv_b + own2_dk_b);
   KvMessage msg = make_kv_message(shape, p.k, p.v, p.mod);
   if (N > 1) {
     for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(dk_b + dv_b), "cudaMalloc(part)");
@@ -818,8 +872,9 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     if (t == 0) {
       p.dk = dk_acc;
       p.dv = dv_acc;
+      const BwdParams first = split ? sub_problem(p, esize, 0, split_b ? b0 : shape->b, 0, split_h ? h0 : shape->h) : p;
       if ((rc = block_mark(ring, 1, stream))) return rc;
-      if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
+      if ((rc = run_bwd_block(first, shape->dtype, stream))) return rc;
       if ((rc = block_mark(ring, 1, stream))) return rc;
       if ((rc = step_done(ring, 0, stream))) return rc;
       if (N > 1 && ring->p2p) {  // the sums of received contributions start after the own block's
@@ -866,9 +921,28 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     if (e != cudaSuccess) return fail_cuda(e, "add");
     if (ring->p2p && (rc = launch_set(ring, ring->reduce_stream, -1, kFlagAdded + me, ring->epoch + t + 1))) return rc;
   }
-  if (N > 1) {
-    RA_CUDA(cudaEventRecord(ring->ev_tail, add_stream), "cudaEventRecord");
-    if ((rc = wait_transfer(ring, stream, ring->ev_tail))) return rc;
+  if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_tail, add_stream), "cudaEventRecord");
+  if (split) {
+    p.k = k_own;
+    p.v = v_own;
+    p.mod = mod_own;
+    p.dk = dk_acc;
+    p.dv = dv_acc;
+    BwdParams second = sub_problem(p, esize, b0, nb2, h0, nh2);
+    second.dk = own2_dk;
+    second.dv = own2_dv;
+    RA_CUDA(cudaMemsetAsync(own2_dk, 0, own2_dk_b + own2_dv_b, stream), "cudaMemsetAsync");
+    count_launch();
+    if ((rc = block_mark(ring, 1, stream))) return rc;
+    if ((rc = run_bwd_block(second, shape->dtype, stream))) return rc;
+    if ((rc = block_mark(ring, 1, stream))) return rc;
+  }
+  if (N > 1 && (rc = wait_transfer(ring, stream, ring->ev_tail))) return rc;
+  if (split) {
+    const int64_t off = ((int64_t)b0 * shape->h + h0) * shape->lk;
+    if ((e = launch_add_f32(dk_acc + off * shape->dk, own2_dk, (int64_t)rows2 * shape->dk, stream)) != cudaSuccess ||
+        (e = launch_add_f32(dv_acc + off * shape->dv, own2_dv, (int64_t)rows2 * shape->dv, stream)) != cudaSuccess)
+      return fail_cuda(e, "add");
   }
   if ((e = launch_cast_from_f32(shape->b, shape->h, shape->lq, shape->dk, dq_acc, tv(dq), shape->dtype, stream)) != cudaSuccess ||
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dk, dk_acc, tv(dk), shape->dtype, stream)) != cudaSuccess ||

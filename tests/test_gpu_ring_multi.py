@@ -30,19 +30,20 @@ def _worker(rank, world, port, case, q_out):
         if "nccl" in mask:  # the NCCL send/recv transport instead of the default peer copies
             os.environ["RA_TRANSPORT"] = "nccl"
         dtype = getattr(torch, dtype)
-        q, k, v, do, rng = make_inputs(5, 2, lq, lk, h, d, dtype)
-        seg = rng.integers(0, 3, (2, max(lq, lk))).astype(np.int32)
+        nb = 1 if "b1" in mask else 2  # one batch element: the backward splits its own block by heads, or not at all
+        q, k, v, do, rng = make_inputs(5, nb, lq, lk, h, d, dtype)
+        seg = rng.integers(0, 3, (nb, max(lq, lk))).astype(np.int32)
         cq, ck = lq // world, lk // world
         sq, sk = slice(rank * cq, (rank + 1) * cq), slice(rank * ck, (rank + 1) * ck)
         if "zigzag" in mask:  # rank r holds chunks r and 2N-1-r; positions say where each token is
             sq = ra.zigzag_indices(lq, rank, world).numpy()
             sk = ra.zigzag_indices(lk, rank, world).numpy()
-        qpos = np.broadcast_to(np.arange(lq, dtype=np.int32), (2, lq))
-        kpos = np.broadcast_to(np.arange(lk, dtype=np.int32), (2, lk))
+        qpos = np.broadcast_to(np.arange(lq, dtype=np.int32), (nb, lq))
+        kpos = np.broadcast_to(np.arange(lk, dtype=np.int32), (nb, lk))
         bias, fn, qkw, kkw = None, None, None, None
         if mask != "none":
             use_seg = "seg" in mask
-            bias = O.score_mod_bias(2, h, qpos, kpos, seg[:, :lq] if use_seg else None, seg[:, :lk] if use_seg else None,
+            bias = O.score_mod_bias(nb, h, qpos, kpos, seg[:, :lq] if use_seg else None, seg[:, :lk] if use_seg else None,
                                     causal="causal" in mask)
             fn = ra.ScoreMod(causal="causal" in mask)
             T = lambda a: to_dev(a, torch.int32)
@@ -81,6 +82,8 @@ CASES = [
     ("bfloat16", 4096, 4096, 2, 128, "causal+zigzag", "tcgen05"),
     ("bfloat16", 2048, 2048, 2, 64, "causal+seg+zigzag", "tcgen05"),
     ("bfloat16", 2048, 2048, 2, 128, "causal+zigzag+nccl", "tcgen05"),
+    ("bfloat16", 2048, 2048, 2, 128, "causal+zigzag+b1", "tcgen05"),
+    ("float32", 256, 256, 1, 32, "causal+b1", "simt"),
 ]
 
 
