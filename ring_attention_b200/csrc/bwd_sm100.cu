@@ -54,6 +54,10 @@ namespace {
 #define TRACE(who, tag) do {} while (0)
 #endif
 constexpr float kLog2e = 1.4426950408889634f;
+#ifndef RA_POLL_NS
+#define RA_POLL_NS 100
+#endif
+constexpr unsigned kProducerPollNs = RA_POLL_NS;
 
 struct BwdTcParams {
   CUtensorMap map_q, map_k, map_v, map_do;
@@ -214,7 +218,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       }
       if (ready) {
         t0 = 0;
-      } else if ((++idle & 63u) == 0) {  // bounded polling
+      } else {
+        // every poll is a shared-memory access, and the MMAs need that bandwidth: poll about every 100 ns
+        __nanosleep(kProducerPollNs);
+      }
+      if (!ready && (++idle & 63u) == 0) {  // bounded polling
         uint32_t stop = 0;
         if (lane == 0) {
           const long long now = clock64();
@@ -682,7 +690,7 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
   cudaError_t e;
   if (p.mod.kinds & kMetaKinds) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
-    if ((e = cudaMallocAsync((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
+    if ((e = scratch_alloc((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
     TileMeta* mq = meta;
     TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
     if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess) return e;

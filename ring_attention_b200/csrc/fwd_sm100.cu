@@ -17,6 +17,7 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "host_util.h"
 #include "tc_common.cuh"
@@ -467,6 +468,36 @@ cudaError_t launch_fwd(const FwdTcParams& P, cudaStream_t s) {
 
 }  // namespace
 
+cudaError_t scratch_alloc(void** ptr, size_t bytes, cudaStream_t s) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static cudaMemPool_t pools[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  cudaMemPool_t pool;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!pools[dev]) {
+      cudaMemPoolProps props;
+      memset(&props, 0, sizeof(props));
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = dev;
+      if ((e = cudaMemPoolCreate(&pools[dev], &props)) != cudaSuccess) {
+        pools[dev] = nullptr;
+        return e;
+      }
+      uint64_t keep = UINT64_MAX;
+      if ((e = cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep)) != cudaSuccess) return e;
+    }
+    pool = pools[dev];
+  }
+  return cudaMallocFromPoolAsync(ptr, bytes, pool, s);
+}
+
 unsigned int* device_status_word() {
   unsigned int* ptr = nullptr;
   if (cudaGetSymbolAddress((void**)&ptr, g_status_word) != cudaSuccess) return nullptr;
@@ -538,7 +569,7 @@ cudaError_t tc_fwd_block(const FwdParams& p, cudaStream_t s) {
   cudaError_t e;
   if (p.mod.kinds & kMetaKinds) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
-    if ((e = cudaMallocAsync((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
+    if ((e = scratch_alloc((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
     TileMeta* mq = meta;
     TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
     if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess) return e;

@@ -101,6 +101,12 @@ bool make_tile_map(CUtensorMap* map, const TensorView& t, int b, int len, int h,
 cudaError_t launch_tile_meta(TileMeta* out, const int32_t* pos, const int32_t* seg, const uint8_t* pre,
                              int b, int len, cudaStream_t s);
 
+// Stream-ordered scratch (tile summaries) from a memory pool of this library, one per device,
+// that keeps what it has been given: the default pool hands unused memory back to the driver at
+// every synchronisation, and the next call's allocation then costs milliseconds on the stream.
+// Free with cudaFreeAsync on the same stream.
+cudaError_t scratch_alloc(void** ptr, size_t bytes, cudaStream_t s);
+
 // Device status word of the current device (bit set = a bounded wait ran out).
 unsigned int* device_status_word();
 
