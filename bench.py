@@ -420,8 +420,8 @@ def main():
                 "bound": "tensor", "kernel": f"{impl_used} {dom_name} block", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of this kernel from the ncu capture of the 8k-token
-                # case (profiles/tc_bwd_kernel_causal_8k.md: 3.44 GB), scaled by the visible-pair count of a launch
-                "traffic": (3.44e9 * bwd_flops_launch / 1.3746e12) if headline else None,
+                # case (profiles/tc_bwd_kernel_causal_8k.md: 3.00 GB), scaled by the visible-pair count of a launch
+                "traffic": (3.00e9 * bwd_flops_launch / 1.3746e12) if headline else None,
                 "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if dom_ms > 5 else 'burst'}",
                 "launch_ms": dom_ms, "flops_per_launch": dom_flops,
                 "launches_per_step": int(bwd_blocks[1] if backward else fwd_blocks[1]),
