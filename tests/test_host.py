@@ -147,3 +147,25 @@ def test_zigzag_layout_round_trip_and_balance():
         assert max(counts) - min(counts) <= S // n, counts
     with pytest.raises(ValueError):
         ra.zigzag_indices(30, 0, 4)
+
+
+def test_bench_workload_pair_counts():
+    """bench.py counts visible (query, key) pairs exactly; check each mask's closed form against a
+    brute-force count on a small sequence."""
+    import bench
+
+    s = 1536
+    i, j = np.arange(s)[:, None], np.arange(s)[None, :]
+    w = dict(b=1, h=1, d=64, s=s, mask="causal")
+    assert bench.visible_pairs(w) == int((j <= i).sum())
+    w = dict(b=1, h=1, d=64, s=s, mask="alibi+window", window=200)
+    assert bench.visible_pairs(w) == int(((j <= i) & (i - j < 200)).sum())
+    w = dict(b=1, h=1, d=64, s=40000, mask="documents")
+    lens = bench.document_lengths(40000)
+    assert sum(lens) == 40000 and all(512 <= n <= 16384 for n in lens[:-1]) and 1 <= lens[-1] <= 16384
+    seg = np.repeat(np.arange(len(lens)), lens)
+    brute = sum(int(n) * (int(n) + 1) // 2 for n in np.bincount(seg))
+    assert bench.visible_pairs(w) == brute
+    # forward-only workloads count 4d FLOP per pair, the others 14d
+    assert bench.flops(dict(w, backward=False)) * 14 == bench.flops(w) * 4
+    assert bench.metric_name(dict(backward=False)).endswith("fwd_tokens_per_s")
