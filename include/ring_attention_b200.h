@@ -202,6 +202,27 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
                 const ra_tensor_t* dq, const ra_tensor_t* dk, const ra_tensor_t* dv,
                 void* stream);
 
+/* Ring steps that the mask empties.  With document masks or a sliding window most (query shard,
+ * K/V block) pairs of a long ring have no visible pair: the reference still builds the bias tile
+ * and runs the block for them (ring.py:104-132, 183-206); here the block kernels skip every tile
+ * of such a pair, but its K/V block and dK/dV contribution would still cross NVLink.  A plan
+ * records which pairs have a visible pair at all, from 128-token summaries of the positions,
+ * segment ids and prefix masks that every rank contributes.
+ *   ra_ring_plan_create  collective over the ring (every rank calls it with its own shard's
+ *                        arrays and the same shape); all-gathers the summaries and SYNCHRONISES
+ *                        the stream once.  Make it once per set of masks, not per layer.
+ *   ra_ring_use_plan     later ra_ring_fwd / ra_ring_bwd calls on this handle leave out the
+ *                        transfers and block launches of empty pairs (plan == NULL: all run).
+ *                        Every rank must use the same plan, and the masks passed to those calls
+ *                        must be the ones the plan was made from.  The handle does not own the plan.
+ *   ra_ring_plan_need    1 when the queries of q_rank see something in the block of kv_rank. */
+typedef struct ra_ring_plan ra_ring_plan_t;
+int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod_t* mod, void* stream,
+                        ra_ring_plan_t** plan);
+void ra_ring_plan_destroy(ra_ring_plan_t* plan);
+int ra_ring_plan_need(const ra_ring_plan_t* plan, int32_t q_rank, int32_t kv_rank);
+int ra_ring_use_plan(ra_ring_t* ring, const ra_ring_plan_t* plan);
+
 /* Rotate caller-owned buffers one place round the ring (rank i -> rank i+1), the
  * _rotate_block of ring.py:41-55, for the arbitrary-bias_fn path that loops on the host.
  * Sends nbytes from each src[i] and receives into dst[i]; n buffers per call. */

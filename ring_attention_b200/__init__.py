@@ -6,10 +6,10 @@ reference re-exports; the rest is the host plumbing a one-process-per-GPU progra
 from ._lib import LIB_PATH, RingAttentionError
 from .layout import zigzag_indices, zigzag_shard, zigzag_unshard
 from .mesh import Mesh, PartitionSpec, Ring
-from .ring import ScoreMod, bwd_block, fwd_block, ring_attention, ring_self_attention
+from .ring import RingPlan, ScoreMod, bwd_block, fwd_block, make_ring_plan, ring_attention, ring_self_attention
 
 __all__ = [
     "ring_attention", "ring_self_attention", "fwd_block", "bwd_block", "ScoreMod",
     "Mesh", "PartitionSpec", "Ring", "RingAttentionError", "LIB_PATH",
-    "zigzag_indices", "zigzag_shard", "zigzag_unshard",
+    "zigzag_indices", "zigzag_shard", "zigzag_unshard", "RingPlan", "make_ring_plan",
 ]

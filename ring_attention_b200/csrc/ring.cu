@@ -187,8 +187,15 @@ struct IpcBundle {
 }  // namespace ringimpl
 using namespace ringimpl;
 
+// Which (query shard, K/V block) pairs of the ring have a visible pair at all: need[q_rank * n + kv_rank].
+struct ra_ring_plan {
+  int nranks = 1;
+  std::vector<uint8_t> need;
+};
+
 struct ra_ring {
   int rank = 0, nranks = 1, device = 0;
+  const ra_ring_plan* plan = nullptr;  // not owned; NULL: every step runs
   ncclComm_t comm = nullptr;
   cudaStream_t push_stream = nullptr;    // transfers this rank issues (high priority)
   cudaStream_t reduce_stream = nullptr;  // sums of dK/dV contributions this rank receives (p2p)
@@ -223,6 +230,73 @@ struct ra_ring {
 };
 
 namespace ringimpl {
+
+// Position / segment / prefix summary of each run of 128 tokens (the last one may be shorter):
+// one warp per chunk.  Same fields as the block kernels' tile summaries, any length.
+__global__ void plan_meta_kernel(TileMeta* __restrict__ out, const int32_t* __restrict__ pos,
+                                 const int32_t* __restrict__ seg, const uint8_t* __restrict__ pre, int len, int n_chunks) {
+  const int chunk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, bb = blockIdx.y;
+  if (chunk >= n_chunks) return;
+  const int64_t base = (int64_t)bb * len;
+  int pmin = INT32_MAX, pmax = INT32_MIN, smin = INT32_MAX, smax = INT32_MIN, any = 0, all = 1;
+  for (int e = chunk * 128 + lane; e < len && e < chunk * 128 + 128; e += 32) {
+    if (pos) {
+      const int v = pos[base + e];
+      pmin = min(pmin, v);
+      pmax = max(pmax, v);
+    }
+    if (seg) {
+      const int v = seg[base + e];
+      smin = min(smin, v);
+      smax = max(smax, v);
+    }
+    if (pre) {
+      const int v = pre[base + e] != 0;
+      any |= v;
+      all &= v;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    pmin = min(pmin, __shfl_xor_sync(0xffffffffu, pmin, o));
+    pmax = max(pmax, __shfl_xor_sync(0xffffffffu, pmax, o));
+    smin = min(smin, __shfl_xor_sync(0xffffffffu, smin, o));
+    smax = max(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+    any |= __shfl_xor_sync(0xffffffffu, any, o);
+    all &= __shfl_xor_sync(0xffffffffu, all, o);
+  }
+  if (lane == 0) {
+    TileMeta m;
+    m.pos_min = pos ? pmin : 0;
+    m.pos_max = pos ? pmax : 0;
+    m.seg_min = seg ? smin : 0;
+    m.seg_max = seg ? smax : 0;
+    m.pre_any = pre ? any : 0;
+    m.pre_all = pre ? all : 0;
+    m.pos_contig = 0;
+    m.pad1 = 0;
+    out[(int64_t)bb * n_chunks + chunk] = m;
+  }
+}
+
+// all: [nranks][b * (nq + nk)] summaries, the q chunks of a rank first.  need[r * nranks + o] = 1 when
+// some query chunk of rank r and some K/V chunk of rank o (same batch element) are not fully masked.
+__global__ void plan_need_kernel(const TileMeta* __restrict__ all, int nranks, int b, int nq, int nk, uint32_t kinds,
+                                 int32_t window, int* __restrict__ need) {
+  const int r = blockIdx.x / nranks, o = blockIdx.x % nranks;
+  const int64_t per_rank = (int64_t)b * (nq + nk);
+  const TileMeta* mq = all + r * per_rank;
+  const TileMeta* mk = all + o * per_rank + (int64_t)b * nq;
+  int found = 0;
+  const int64_t total = (int64_t)b * nq * nk;
+  for (int64_t i = threadIdx.x; i < total && !found; i += blockDim.x) {
+    const int bb = (int)(i / ((int64_t)nq * nk));
+    const int rem = (int)(i % ((int64_t)nq * nk));
+    if (classify_tiles(kinds, window, mq[bb * nq + rem / nk], mk[bb * nk + rem % nk]) != 0) found = 1;
+  }
+  if (__syncthreads_or(found) && threadIdx.x == 0) need[blockIdx.x] = 1;
+}
 
 struct KvMessage {
   // Flat messages that make up one K/V block: pointers on the sender (own tensors) and
@@ -406,12 +480,13 @@ int ensure_shared(ra_ring_t* r, size_t stage_need, size_t rpart_need) {
   return 0;
 }
 
+// to / from < 0: that half of the exchange is left out (both ends of it agree, see pair_needed)
 int exchange_kv_nccl(ra_ring_t* r, const KvMessage& msg, void* stage, int to, int from) {
   NcclApi* api = nccl_api();
   RA_NCCL(api->GroupStart(), "ncclGroupStart");
   for (int i = 0; i < msg.n; ++i) {
-    RA_NCCL(api->Send(msg.src[i], msg.bytes[i], ncclChar, to, r->comm, r->push_stream), "ncclSend");
-    RA_NCCL(api->Recv((char*)stage + msg.offset[i], msg.bytes[i], ncclChar, from, r->comm, r->push_stream), "ncclRecv");
+    if (to >= 0) RA_NCCL(api->Send(msg.src[i], msg.bytes[i], ncclChar, to, r->comm, r->push_stream), "ncclSend");
+    if (from >= 0) RA_NCCL(api->Recv((char*)stage + msg.offset[i], msg.bytes[i], ncclChar, from, r->comm, r->push_stream), "ncclRecv");
   }
   RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
   return 0;
@@ -419,10 +494,18 @@ int exchange_kv_nccl(ra_ring_t* r, const KvMessage& msg, void* stage, int to, in
 
 // Issue, on the push stream, the transfer that gives the consumer of step t (t >= 1) this
 // rank's K/V block.  Called while step t-1 is being enqueued, so it runs under step t-1.
+// Under a plan a transfer whose consumer has nothing visible in the block is left out, on both
+// sides: sender and receiver read the same matrix.
+bool pair_needed(const ra_ring_t* r, int q_rank, int kv_rank) {
+  return !r->plan || r->plan->need[(size_t)q_rank * r->nranks + kv_rank] != 0;
+}
+
 int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
   const int N = r->nranks, me = r->rank, slot = t & 1;
   const int to = (me + t) % N, from = ((me - t) % N + N) % N;
+  const bool do_send = pair_needed(r, to, me), do_recv = pair_needed(r, me, from);
   if (r->p2p) {
+    if (!do_send) return 0;
     // the consumer's stage[slot] was last read by its step t-2 (or by its previous call)
     const uint64_t need = t >= 3 ? r->epoch + t - 1 : r->epoch;
     int rc;
@@ -434,7 +517,7 @@ int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
   }
   if (t >= 2) RA_CUDA(cudaStreamWaitEvent(r->push_stream, r->ev_done[slot], 0), "cudaStreamWaitEvent");
   int rc;
-  if ((rc = exchange_kv_nccl(r, msg, r->stage[slot], to, from))) return rc;
+  if ((do_send || do_recv) && (rc = exchange_kv_nccl(r, msg, r->stage[slot], do_send ? to : -1, do_recv ? from : -1))) return rc;
   RA_CUDA(cudaEventRecord(r->ev_recv[slot], r->push_stream), "cudaEventRecord");
   return 0;
 }
@@ -691,8 +774,18 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   const TensorView k_own = p.k, v_own = p.v;
   const ModParams mod_own = p.mod;
   const TensorView out_view{out->ptr, out->stride_b, out->stride_l, out->stride_h};
+  if (ring->plan && ring->plan->nranks != N) return fail(-39, "the plan was made for a ring of %d ranks", ring->plan->nranks);
+  const int me_f = ring->rank;
+  auto source = [&](int t) { return ((me_f - t) % N + N) % N; };
+  int t_last = 0;  // last step that runs (the own block always does)
+  for (int t = 1; t < N; ++t)
+    if (pair_needed(ring, me_f, source(t))) t_last = t;
   for (int t = 0; t < N; ++t) {
     if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;  // runs under step t
+    if (t > 0 && !pair_needed(ring, me_f, source(t))) {  // nothing visible in this block: no wait, no launch
+      if ((rc = step_done(ring, t, stream))) return rc;
+      continue;
+    }
     p.k = k_own;
     p.v = v_own;
     p.mod = mod_own;
@@ -701,7 +794,7 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       if ((rc = wait_kv(ring, t, stream))) return rc;
     }
     p.first = (t == 0);
-    if (t == N - 1) {  // the tensor-core kernel normalises and writes out / L itself on the last block
+    if (t == t_last) {  // the tensor-core kernel normalises and writes out / L itself on the last block
       p.final_out = out_view;
       p.final_lse = lse;
     }
@@ -823,6 +916,8 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(dk_b + dv_b), "cudaMalloc(part)");
     if ((rc = ensure_shared(ring, msg.total, dk_b + dv_b))) return rc;
   }
+  if (ring->plan && ring->plan->nranks != ring->nranks)
+    return fail(-39, "the plan was made for a ring of %d ranks", ring->plan->nranks);
   if ((rc = begin_call(ring, 1, stream))) return rc;
 
   cudaError_t e = launch_delta(shape->b, shape->h, shape->lq, shape->dv, tv(out), p.dout,
@@ -884,41 +979,53 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       continue;
     }
     const int slot = t & 1;
-    use_staged(msg, ring->stage[slot], &p.k, &p.v, &p.mod);
-    if ((rc = wait_kv(ring, t, stream))) return rc;
-    // this step's contribution to the remote block's dK/dV, built from zero
-    if (t >= 3) RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
-    p.dk = (float*)ring->part[slot].ptr;
-    p.dv = (float*)((char*)ring->part[slot].ptr + dk_b);
-    RA_CUDA(cudaMemsetAsync(ring->part[slot].ptr, 0, dk_b + dv_b, stream), "cudaMemsetAsync");
-    count_launch();
-    if ((rc = block_mark(ring, 1, stream))) return rc;
-    if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
-    if ((rc = block_mark(ring, 1, stream))) return rc;
-    if ((rc = step_done(ring, t, stream))) return rc;
-    RA_CUDA(cudaEventRecord(ring->ev_part[slot], stream), "cudaEventRecord");
-    // give it to the block's owner; take what another rank computed for this rank's block
-    RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
     const int owner = ((me - t) % N + N) % N, giver = (me + t) % N;
+    // Under a plan: this rank computes (and gives) only where its queries see the block, and
+    // receives only where the giver's queries see this rank's block.
+    const bool compute = pair_needed(ring, me, owner), receive = pair_needed(ring, giver, me);
+    if (compute) {
+      use_staged(msg, ring->stage[slot], &p.k, &p.v, &p.mod);
+      if ((rc = wait_kv(ring, t, stream))) return rc;
+      // this step's contribution to the remote block's dK/dV, built from zero
+      if (t >= 3) RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
+      p.dk = (float*)ring->part[slot].ptr;
+      p.dv = (float*)((char*)ring->part[slot].ptr + dk_b);
+      RA_CUDA(cudaMemsetAsync(ring->part[slot].ptr, 0, dk_b + dv_b, stream), "cudaMemsetAsync");
+      count_launch();
+      if ((rc = block_mark(ring, 1, stream))) return rc;
+      if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
+      if ((rc = block_mark(ring, 1, stream))) return rc;
+    }
+    if ((rc = step_done(ring, t, stream))) return rc;
+    if (compute) {
+      RA_CUDA(cudaEventRecord(ring->ev_part[slot], stream), "cudaEventRecord");
+      // give it to the block's owner; take what another rank computed for this rank's block
+      RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
+    }
     if (ring->p2p) {
-      // the owner's rpart[slot] is free once it has summed the contribution of step t-2
-      const uint64_t need = t >= 3 ? ring->epoch + t - 1 : ring->epoch;
-      if ((rc = launch_wait(ring, ring->push_stream, kFlagAdded + owner, need))) return rc;
-      RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
-                              cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
-      if ((rc = launch_set(ring, ring->push_stream, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
-      RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
+      if (compute) {
+        // the owner's rpart[slot] is free once it has summed the contribution of step t-2
+        const uint64_t need = t >= 3 ? ring->epoch + t - 1 : ring->epoch;
+        if ((rc = launch_wait(ring, ring->push_stream, kFlagAdded + owner, need))) return rc;
+        RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
+                                cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
+        if ((rc = launch_set(ring, ring->push_stream, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
+        RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
+      }
       // owner side, on the reduce stream
-      if ((rc = launch_wait(ring, ring->reduce_stream, kFlagPartReady + slot, ring->epoch + t))) return rc;
-    } else {
+      if (receive && (rc = launch_wait(ring, ring->reduce_stream, kFlagPartReady + slot, ring->epoch + t))) return rc;
+    } else if (compute || receive) {
       RA_NCCL(api->GroupStart(), "ncclGroupStart");
-      RA_NCCL(api->Send(ring->part[slot].ptr, dk_b + dv_b, ncclChar, owner, ring->comm, ring->push_stream), "ncclSend");
-      RA_NCCL(api->Recv(ring->rpart[slot], dk_b + dv_b, ncclChar, giver, ring->comm, ring->push_stream), "ncclRecv");
+      if (compute) RA_NCCL(api->Send(ring->part[slot].ptr, dk_b + dv_b, ncclChar, owner, ring->comm, ring->push_stream), "ncclSend");
+      if (receive) RA_NCCL(api->Recv(ring->rpart[slot], dk_b + dv_b, ncclChar, giver, ring->comm, ring->push_stream), "ncclRecv");
       RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
       RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
     }
-    e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot], (int64_t)((dk_b + dv_b) / 4), add_stream);
-    if (e != cudaSuccess) return fail_cuda(e, "add");
+    if (receive) {
+      e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot], (int64_t)((dk_b + dv_b) / 4), add_stream);
+      if (e != cudaSuccess) return fail_cuda(e, "add");
+    }
+    // published even when nothing was received: it is what frees rpart[slot] for the step after next
     if (ring->p2p && (rc = launch_set(ring, ring->reduce_stream, -1, kFlagAdded + me, ring->epoch + t + 1))) return rc;
   }
   if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_tail, add_stream), "cudaEventRecord");
@@ -949,6 +1056,89 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dv, dv_acc, tv(dv), shape->dtype, stream)) != cudaSuccess)
     return fail_cuda(e, "cast");
   return end_call(ring, 1, stream);
+}
+
+int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod_t* mod, void* stream_,
+                        ra_ring_plan_t** out) {
+  int rc;
+  if (!ring) return fail(-30, "ring handle is NULL");
+  if (!out) return fail(-6, "plan result pointer is NULL");
+  *out = nullptr;
+  if ((rc = check_shape(shape))) return rc;
+  ModParams m;
+  if ((rc = check_mod(mod, &m))) return rc;
+  const int N = ring->nranks;
+  ra_ring_plan* plan = new ra_ring_plan;
+  plan->nranks = N;
+  plan->need.assign((size_t)N * N, 1);
+  // without a mask every pair has visible pairs; a dense bias tile cannot be summarised
+  if (N == 1 || !(m.kinds & kMaskKinds) || (m.kinds & RA_MOD_DENSE)) {
+    *out = plan;
+    return 0;
+  }
+  cudaStream_t s = (cudaStream_t)stream_;
+  const int b = shape->b, nq = (shape->lq + 127) / 128, nk = (shape->lk + 127) / 128;
+  const size_t per_rank = (size_t)b * (nq + nk);
+  TileMeta *mine = nullptr, *all = nullptr;
+  int* need_dev = nullptr;
+  std::vector<int> need_host((size_t)N * N, 1);
+  auto cleanup = [&]() {
+    if (mine) cudaFree(mine);
+    if (all) cudaFree(all);
+    if (need_dev) cudaFree(need_dev);
+  };
+  auto bail = [&](int code) {
+    cleanup();
+    delete plan;
+    return code;
+  };
+  cudaError_t e;
+  if ((e = cudaMalloc((void**)&mine, per_rank * sizeof(TileMeta))) != cudaSuccess ||
+      (e = cudaMalloc((void**)&all, per_rank * sizeof(TileMeta) * N)) != cudaSuccess ||
+      (e = cudaMalloc((void**)&need_dev, sizeof(int) * N * N)) != cudaSuccess)
+    return bail(fail_cuda(e, "cudaMalloc(plan)"));
+  plan_meta_kernel<<<dim3((nq + 7) / 8, b), 256, 0, s>>>(mine, m.q_pos, m.q_seg, m.q_pre, shape->lq, nq);
+  plan_meta_kernel<<<dim3((nk + 7) / 8, b), 256, 0, s>>>(mine + (size_t)b * nq, m.kv_pos, m.kv_seg, m.kv_pre, shape->lk, nk);
+  count_launch(2);
+  if ((e = cudaGetLastError()) != cudaSuccess) return bail(fail_cuda(e, "plan_meta_kernel"));
+  // the communicator's other traffic runs on the push stream: order the all-gather after it
+  if ((e = cudaEventRecord(ring->ev_push_tail, ring->push_stream)) != cudaSuccess ||
+      (e = cudaStreamWaitEvent(s, ring->ev_push_tail, 0)) != cudaSuccess)
+    return bail(fail_cuda(e, "cudaStreamWaitEvent"));
+  NcclApi* api = nccl_api();
+  ncclResult_t nr = api->AllGather(mine, all, per_rank * sizeof(TileMeta), ncclChar, ring->comm, s);
+  if (nr != ncclSuccess) return bail(fail_nccl(nr, "ncclAllGather(plan)"));
+  if ((e = cudaMemsetAsync(need_dev, 0, sizeof(int) * N * N, s)) != cudaSuccess) return bail(fail_cuda(e, "cudaMemsetAsync"));
+  plan_need_kernel<<<N * N, 256, 0, s>>>(all, N, b, nq, nk, m.kinds, m.window, need_dev);
+  count_launch();
+  if ((e = cudaGetLastError()) != cudaSuccess) return bail(fail_cuda(e, "plan_need_kernel"));
+  if ((e = cudaMemcpyAsync(need_host.data(), need_dev, sizeof(int) * N * N, cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+      (e = cudaStreamSynchronize(s)) != cudaSuccess)
+    return bail(fail_cuda(e, "plan readback"));
+  // later NCCL traffic on the push stream comes after the all-gather
+  if ((e = cudaEventRecord(ring->ev_start, s)) != cudaSuccess ||
+      (e = cudaStreamWaitEvent(ring->push_stream, ring->ev_start, 0)) != cudaSuccess)
+    return bail(fail_cuda(e, "cudaStreamWaitEvent"));
+  for (size_t i = 0; i < need_host.size(); ++i) plan->need[i] = need_host[i] ? 1 : 0;
+  for (int r = 0; r < N; ++r) plan->need[(size_t)r * N + r] = 1;  // the own block always runs
+  cleanup();
+  *out = plan;
+  return 0;
+}
+
+void ra_ring_plan_destroy(ra_ring_plan_t* plan) { delete plan; }
+
+int ra_ring_plan_need(const ra_ring_plan_t* plan, int32_t q_rank, int32_t kv_rank) {
+  if (!plan) return fail(-6, "plan is NULL");
+  if (q_rank < 0 || kv_rank < 0 || q_rank >= plan->nranks || kv_rank >= plan->nranks) return fail(-33, "bad rank");
+  return plan->need[(size_t)q_rank * plan->nranks + kv_rank];
+}
+
+int ra_ring_use_plan(ra_ring_t* ring, const ra_ring_plan_t* plan) {
+  if (!ring) return fail(-30, "ring handle is NULL");
+  if (plan && plan->nranks != ring->nranks) return fail(-39, "the plan was made for a ring of %d ranks", plan->nranks);
+  ring->plan = plan;
+  return 0;
 }
 
 int ra_ring_rotate(ra_ring_t* ring, int32_t n, const void* const* src, void* const* dst,

@@ -360,19 +360,77 @@ def _host_bwd(ring, q, k, v, out, lse, do, sm_scale, bias_fn, q_kwargs, kv_kwarg
     return cast(dq, q, lq), cast(dkk, k, lk), cast(dvv, v, lk)
 
 
+class RingPlan:
+    """Which (query shard, K/V block) pairs of a ring have a visible pair at all under a
+    `ScoreMod` mask.  With document masks or a sliding window most pairs of a long ring have
+    none; `ring_attention(..., plan=plan)` then leaves out their transfers and block launches
+    (the reference runs every step, ring.py:104-132).  Made by `make_ring_plan`, collectively,
+    once per set of masks: it synchronises the stream once.  The masks of every call that uses
+    the plan must be the ones it was made from."""
+
+    def __init__(self, ring: Ring, handle):
+        self.ring, self.handle = ring, handle
+
+    def needed(self, q_rank: int, kv_rank: int) -> bool:
+        r = lib.ra_ring_plan_need(self.handle, q_rank, kv_rank)
+        check(min(r, 0))
+        return r == 1
+
+    def matrix(self):
+        n = self.ring.size
+        return [[self.needed(r, o) for o in range(n)] for r in range(n)]
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib.ra_ring_plan_destroy(self.handle)
+            self.handle = None
+
+
+def make_ring_plan(q: torch.Tensor, k: torch.Tensor, axis_name, bias_fn, bias_q_kwargs: Optional[dict] = None,
+                   bias_kv_kwargs: Optional[dict] = None) -> RingPlan:
+    """Plan for ring attention calls with these shard shapes ([b, l, h, d]) and this mask.
+    Every rank of the ring must call it (it all-gathers 128-token summaries of the positions,
+    segment ids and prefix masks)."""
+    if bias_fn is not None and not isinstance(bias_fn, ScoreMod):
+        raise ValueError("a plan needs a ScoreMod bias_fn (or None): a callable's bias cannot be summarised")
+    ring = resolve_axis(axis_name)
+    b, lq, h, dk = q.shape
+    mod = _ModArgs(bias_fn, bias_q_kwargs or {}, bias_kv_kwargs or {}, h)
+    sh = _shape(b, h, lq, k.shape[1], dk, dk, _dtype_code(q), 1.0)
+    handle = C.c_void_p()
+    check(lib.ra_ring_plan_create(ring.handle, C.byref(sh), mod.ref(), _stream(), C.byref(handle)))
+    return RingPlan(ring, handle)
+
+
+class _UsePlan:
+    """Applies a plan to a ring handle for the calls inside the `with` block."""
+
+    def __init__(self, ring: Ring, plan: Optional[RingPlan]):
+        self.ring, self.plan = ring, plan
+
+    def __enter__(self):
+        if self.plan is not None:
+            check(lib.ra_ring_use_plan(self.ring.handle, self.plan.handle))
+
+    def __exit__(self, *exc):
+        if self.plan is not None:
+            check(lib.ra_ring_use_plan(self.ring.handle, None))
+
+
 class _RingAttention(torch.autograd.Function):
     """The custom-VJP boundary of ring.py:214-243: gradients flow to q, k, v only."""
 
     @staticmethod
-    def forward(ctx, q, k, v, ring, sm_scale, bias_fn, q_kwargs, kv_kwargs, impl):
+    def forward(ctx, q, k, v, ring, sm_scale, bias_fn, q_kwargs, kv_kwargs, impl, plan):
         q, k, v = _blhd(q), _blhd(k), _blhd(v)
         fused = bias_fn is None or isinstance(bias_fn, ScoreMod)
         check(lib.ra_set_impl(impl))
         fwd = _fused_fwd if fused else _host_fwd
-        out, lse = fwd(ring, q, k, v, sm_scale, bias_fn, q_kwargs, kv_kwargs)
+        with _UsePlan(ring, plan if fused else None):
+            out, lse = fwd(ring, q, k, v, sm_scale, bias_fn, q_kwargs, kv_kwargs)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.ring, ctx.sm_scale, ctx.bias_fn, ctx.impl, ctx.fused = ring, sm_scale, bias_fn, impl, fused
-        ctx.q_kwargs, ctx.kv_kwargs = q_kwargs, kv_kwargs
+        ctx.q_kwargs, ctx.kv_kwargs, ctx.plan = q_kwargs, kv_kwargs, plan
         return out
 
     @staticmethod
@@ -381,8 +439,9 @@ class _RingAttention(torch.autograd.Function):
         do = _blhd(do)
         check(lib.ra_set_impl(ctx.impl))
         bwd = _fused_bwd if ctx.fused else _host_bwd
-        dq, dk, dv = bwd(ctx.ring, q, k, v, out, lse, do, ctx.sm_scale, ctx.bias_fn, ctx.q_kwargs, ctx.kv_kwargs)
-        return dq, dk, dv, None, None, None, None, None, None
+        with _UsePlan(ctx.ring, ctx.plan if ctx.fused else None):
+            dq, dk, dv = bwd(ctx.ring, q, k, v, out, lse, do, ctx.sm_scale, ctx.bias_fn, ctx.q_kwargs, ctx.kv_kwargs)
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
 def ring_attention(
@@ -395,8 +454,9 @@ def ring_attention(
     bias_kv_kwargs: Optional[dict] = None,
     sm_scale: Optional[float] = None,
     block_impl: str = "cuda",
+    plan: Optional["RingPlan"] = None,
 ) -> torch.Tensor:
-    """Ring attention on this process's shard: the signature of ring.py:246-256.
+    """Ring attention on this process's shard: the signature of ring.py:246-256, plus `plan`.
 
     q [b, lq, h, dk], k [b, lk, h, dk], v [b, lk, h, dv] are this rank's blocks of arrays
     sharded on the length axis.  `axis_name` names an axis of the active `Mesh` (or is a
@@ -406,6 +466,8 @@ def ring_attention(
     callable is honoured through a dense tile per ring step.  `block_impl`: "cuda"
     (default: tcgen05 kernels when the shape fits, fp32 CUDA-core kernels otherwise),
     "tcgen05", "simt"; the reference's "pallas"/"jax" are accepted as "cuda".
+    `plan` (from `make_ring_plan`, optional) leaves out the ring steps whose block the mask
+    empties; without it every step runs, as in the reference.
     Every rank of the ring must make the same call.
     """
     if sm_scale is None:
@@ -421,7 +483,7 @@ def ring_attention(
         raise ValueError("q, k and v must have the same number of heads")
     ring = resolve_axis(axis_name)
     return _RingAttention.apply(q, k, v, ring, float(sm_scale), bias_fn, bias_q_kwargs, bias_kv_kwargs,
-                                _IMPLS[block_impl])
+                                _IMPLS[block_impl], plan)
 
 
 def ring_self_attention(

@@ -33,19 +33,25 @@ def _worker(rank, world, port, case, q_out):
         nb = 1 if "b1" in mask else 2  # one batch element: the backward splits its own block by heads, or not at all
         q, k, v, do, rng = make_inputs(5, nb, lq, lk, h, d, dtype)
         seg = rng.integers(0, 3, (nb, max(lq, lk))).astype(np.int32)
+        import re
+
         cq, ck = lq // world, lk // world
-        sq, sk = slice(rank * cq, (rank + 1) * cq), slice(rank * ck, (rank + 1) * ck)
-        if "zigzag" in mask:  # rank r holds chunks r and 2N-1-r; positions say where each token is
-            sq = ra.zigzag_indices(lq, rank, world).numpy()
-            sk = ra.zigzag_indices(lk, rank, world).numpy()
+
+        def shard_of(r):
+            if "zigzag" in mask:  # rank r holds chunks r and 2N-1-r; positions say where each token is
+                return ra.zigzag_indices(lq, r, world).numpy(), ra.zigzag_indices(lk, r, world).numpy()
+            return np.arange(r * cq, (r + 1) * cq), np.arange(r * ck, (r + 1) * ck)
+
+        sq, sk = shard_of(rank)
+        window = int(re.search(r"window(\d+)", mask).group(1)) if "window" in mask else 0
         qpos = np.broadcast_to(np.arange(lq, dtype=np.int32), (nb, lq))
         kpos = np.broadcast_to(np.arange(lk, dtype=np.int32), (nb, lk))
         bias, fn, qkw, kkw = None, None, None, None
         if mask != "none":
             use_seg = "seg" in mask
             bias = O.score_mod_bias(nb, h, qpos, kpos, seg[:, :lq] if use_seg else None, seg[:, :lk] if use_seg else None,
-                                    causal="causal" in mask)
-            fn = ra.ScoreMod(causal="causal" in mask)
+                                    causal="causal" in mask, window=window)
+            fn = ra.ScoreMod(causal="causal" in mask, window=window)
             T = lambda a: to_dev(a, torch.int32)
             qkw = {"q_positions": T(qpos[:, sq]), "q_segment_ids": T(seg[:, :lq][:, sq]) if use_seg else None}
             kkw = {"kv_positions": T(kpos[:, sk]), "kv_segment_ids": T(seg[:, :lk][:, sk]) if use_seg else None}
@@ -53,10 +59,23 @@ def _worker(rank, world, port, case, q_out):
             pass
         with ra.Mesh((1, world), ("dp", "sp")):
             tq, tk, tv = (to_dev(x, dtype).requires_grad_(True) for x in (q[:, sq], k[:, sk], v[:, sk]))
+            plan = None
+            if "plan" in mask:  # leave out the ring steps whose block the mask empties
+                plan = ra.make_ring_plan(tq, tk, "sp", fn, qkw, kkw)
+                vis = np.isfinite(bias).any(axis=(0, 1))  # [lq, lk]
+                want = [[bool(vis[np.ix_(shard_of(r)[0], shard_of(o)[1])].any()) or r == o for o in range(world)]
+                        for r in range(world)]
+                got = plan.matrix()
+                # the plan works on 128-token summaries: it may keep a pair that is in fact empty, never drop one
+                for r in range(world):
+                    for o in range(world):
+                        assert got[r][o] or not want[r][o], f"plan drops pair ({r}, {o}) that has visible pairs"
+                if not all(map(all, want)):
+                    assert sum(map(sum, got)) < world * world, "the plan keeps every pair although some are empty"
             for rep in range(2):  # second pass reuses the ring's buffers
                 tq.grad = tk.grad = tv.grad = None
                 out = ra.ring_attention(tq, tk, tv, "sp", bias_fn=fn, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
-                                        block_impl=impl)
+                                        block_impl=impl, plan=plan)
                 out.backward(to_dev(do[:, sq], dtype))
             torch.cuda.synchronize()
         ref = O.mha(q, k, v, bias)
@@ -84,6 +103,9 @@ CASES = [
     ("bfloat16", 2048, 2048, 2, 128, "causal+zigzag+nccl", "tcgen05"),
     ("bfloat16", 2048, 2048, 2, 128, "causal+zigzag+b1", "tcgen05"),
     ("float32", 256, 256, 1, 32, "causal+b1", "simt"),
+    ("bfloat16", 2048, 2048, 2, 128, "causal+window256+plan", "tcgen05"),
+    ("bfloat16", 4096, 4096, 2, 128, "causal+window300+zigzag+plan", "tcgen05"),
+    ("float32", 512, 512, 2, 32, "causal+window100+plan+nccl", "simt"),
 ]
 
 
