@@ -214,7 +214,7 @@ def workload_config(args, w, n):
         "workload": f"{args.workload}: {w['dtype']} {what} MHA {'fwd+bwd' if w.get('backward', True) else 'fwd'}, "
                     f"batch {w['b']}, heads {w['h']}, head_dim {w['d']}, total seq {w['s']} sharded evenly over {n} GPU(s)",
         "global_batch": w["b"], "seq_len": w["s"], "heads": w["h"], "head_dim": w["d"],
-        "parallelism": f"sp{n}", "layout": args.layout if n > 1 else "contiguous", "l2": "inputs larger than L2 (each of q,k,v,dO per rank exceeds 126 MB at N<=2; "
+        "parallelism": f"sp{n}", "layout": args.layout if n > 1 else "contiguous", "plan": bool(args.plan and n > 1), "l2": "inputs larger than L2 (each of q,k,v,dO per rank exceeds 126 MB at N<=2; "
                                       "an L2 flush runs between steps otherwise)",
     }
 
@@ -229,6 +229,8 @@ def main():
     ap.add_argument("--block-impl", default="cuda", choices=["cuda", "simt", "tcgen05"])
     ap.add_argument("--layout", default="zigzag", choices=["zigzag", "contiguous"],
                     help="token->rank layout at N>1: zigzag balances causal work, contiguous is the reference tests' layout")
+    ap.add_argument("--plan", action="store_true",
+                    help="at N>1: leave out the ring steps whose block the mask empties (made once, before the warm-up)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -297,6 +299,17 @@ def main():
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if q.numel() * q.element_size() < (126 << 20) else None
 
+    # the public API's view of the same mask (used by the plan and by the e2e leg)
+    qkw = {"q_positions": pos}
+    kkw = {"kv_positions": pos}
+    if seg is not None:
+        qkw["q_segment_ids"] = seg
+        kkw["kv_segment_ids"] = seg
+    sm = ra.ScoreMod(causal=True, alibi_slopes=slopes, window=w.get("window", 0))
+    plan = ra.make_ring_plan(q, k, ring, sm, qkw, kkw) if (args.plan and N > 1) else None
+    if plan is not None:
+        check(lib.ra_ring_use_plan(ring.handle, plan.handle))
+
     def step():
         check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
         if backward:
@@ -358,12 +371,8 @@ def main():
     if not args.no_e2e:
         host_in = host if backward else host[:3]
         host_out = [torch.empty((b, c, h, d), dtype=dt).pin_memory() for _ in range(4 if backward else 1)]
-        qkw = {"q_positions": pos}
-        kkw = {"kv_positions": pos}
-        if seg is not None:
-            qkw["q_segment_ids"] = seg
-            kkw["kv_segment_ids"] = seg
-        sm = ra.ScoreMod(causal=True, alibi_slopes=slopes, window=w.get("window", 0))
+        if plan is not None:
+            check(lib.ra_ring_use_plan(ring.handle, None))  # the public API applies the plan per call
 
         # Every step copies its inputs from pinned host memory and its results back.  The copies
         # run on streams of their own (the host->device and device->host copy engines work next
@@ -396,7 +405,7 @@ def main():
                 main.wait_event(ev_in[slot])
                 dev = [t.detach().requires_grad_(backward) for t in dev_in[slot][:3]]
                 o = ra.ring_attention(dev[0], dev[1], dev[2], ring, bias_fn=sm, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
-                                      block_impl=args.block_impl)
+                                      block_impl=args.block_impl, plan=plan)
                 if backward:
                     o.backward(dev_in[slot][3])
                 ev_free[slot].record(main)
@@ -461,6 +470,7 @@ def main():
             "exposed_comm_ms": max(exposed_all), "exposed_comm_frac": max(exposed_all) / step_ms,
             "exposed_comm_ms_per_rank": exposed_all,
             "gpu_launches": int(launches),
+            "ring_plan": plan.matrix() if plan is not None else None,
             "clocks": clocks.summary(),
         }
         if e2e is not None:
