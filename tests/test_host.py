@@ -72,6 +72,12 @@ def test_argument_errors_are_negative_and_explained():
     assert lib.ra_set_impl(_lib.RA_IMPL_AUTO) == 0
     assert lib.ra_ring_source(0, 0, 0) < 0
     assert lib.ra_ring_fwd(None, C.byref(_shape()), *args, None, C.byref(t), one, None) == -30
+    # ring plans: handle and result pointer are checked before anything touches a device
+    out = C.c_void_p()
+    assert lib.ra_ring_plan_create(None, C.byref(_shape()), None, None, C.byref(out)) == -30 and not out.value
+    assert lib.ra_ring_use_plan(None, None) == -30
+    assert lib.ra_ring_plan_need(None, 0, 0) == -6
+    lib.ra_ring_plan_destroy(None)  # like free(NULL)
 
 
 def test_ring_source_matches_reference_rotation():
