@@ -18,15 +18,21 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _exchange(send_arr, to, frm):
+def _exchange(send_arr, to, frm, do_send=True, do_recv=True):
+    """One ring exchange; either half can be left out (both of its ends must agree)."""
     recv = torch.empty_like(send_arr)
-    ops = [dist.P2POp(dist.isend, send_arr, to), dist.P2POp(dist.irecv, recv, frm)]
-    for w in dist.batch_isend_irecv(ops):
-        w.wait()
-    return recv
+    ops = []
+    if do_send:
+        ops.append(dist.P2POp(dist.isend, send_arr, to))
+    if do_recv:
+        ops.append(dist.P2POp(dist.irecv, recv, frm))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    return recv if do_recv else None
 
 
-def _worker(rank, world, port, q_out):
+def _worker(rank, world, port, q_out, window=0, plan=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -48,6 +54,18 @@ def _worker(rank, world, port, q_out):
     o = np.zeros_like(ql)
     m = np.full(ql.shape[:3], -np.inf)
     l = np.zeros(ql.shape[:3])
+
+    def mask_bias(qp, kp):
+        return O.score_mod_bias(b, 1, qp, kp, None, None, causal=True, window=window)
+
+    bias_full = mask_bias(pos, pos)
+    # The plan of the CUDA schedule: need[r][o] says whether the queries of rank r see anything in
+    # the block of rank o.  Every rank holds the same matrix, so the two ends of a transfer agree.
+    vis = np.isfinite(bias_full).any(axis=(0, 1))
+    need = [[(not plan) or r == o_ or bool(vis[r * c:(r + 1) * c, o_ * c:(o_ + 1) * c].any()) for o_ in range(world)]
+            for r in range(world)]
+    if plan:
+        assert not all(map(all, need)), "this mask should empty at least one pair"
     blocks = []
     for t in range(world):
         src = lib.ra_ring_source(rank, world, t)
@@ -56,10 +74,13 @@ def _worker(rank, world, port, q_out):
         else:  # the owner sends straight to its consumer
             to, frm = (rank + t) % world, (rank - t) % world
             assert frm == src
-            kt = _exchange(torch.from_numpy(kl), to, frm).numpy()
-            vt = _exchange(torch.from_numpy(vl), to, frm).numpy()
-            pt = _exchange(torch.from_numpy(kpos), to, frm).numpy()
-        bias = O.self_attention_bias(True, q_positions=qpos, kv_positions=pt)
+            snd, rcv = need[to][rank], need[rank][frm]
+            kt, vt, pt = (_exchange(torch.from_numpy(x), to, frm, snd, rcv) for x in (kl, vl, kpos))
+            if not rcv:  # nothing visible in this block: no wait, no block update
+                blocks.append(None)
+                continue
+            kt, vt, pt = kt.numpy(), vt.numpy(), pt.numpy()
+        bias = mask_bias(qpos, pt)
         o, m, l = O.fwd_block(ql, kt, vt, bias, o, m, l, scale)
         blocks.append((kt, vt, bias))
     out, L = O.finalize(o, m, l)
@@ -67,17 +88,21 @@ def _worker(rank, world, port, q_out):
     dk = np.zeros_like(kl)
     dv = np.zeros_like(vl)
     for t in range(world):
-        kt, vt, bias = blocks[t]
-        dq_, dk_, dv_ = O.bwd_block(ql, kt, vt, bias, out, L, dol, scale)
-        dq += dq_
+        owner, giver = (rank - t) % world, (rank + t) % world
+        compute, receive = blocks[t] is not None, need[giver][rank]
+        dk_ = dv_ = np.zeros_like(kl)
+        if compute:
+            kt, vt, bias = blocks[t]
+            dq_, dk_, dv_ = O.bwd_block(ql, kt, vt, bias, out, L, dol, scale)
+            dq += dq_
         if t == 0:
             dk += dk_
             dv += dv_
         else:  # contribution goes to the owner (rank - t), ours comes from rank + t
-            owner, giver = (rank - t) % world, (rank + t) % world
-            dk += _exchange(torch.from_numpy(np.ascontiguousarray(dk_)), owner, giver).numpy()
-            dv += _exchange(torch.from_numpy(np.ascontiguousarray(dv_)), owner, giver).numpy()
-    bias_full = O.self_attention_bias(True, q_positions=pos, kv_positions=pos)
+            got = [_exchange(torch.from_numpy(np.ascontiguousarray(x)), owner, giver, compute, receive) for x in (dk_, dv_)]
+            if receive:
+                dk += got[0].numpy()
+                dv += got[1].numpy()
     ref = O.mha(q, k, v, bias_full)
     rq, rk, rv = O.mha_grads(q, k, v, do, bias_full)
     un = lambda x: np.transpose(x, (0, 2, 1, 3))
@@ -89,12 +114,14 @@ def _worker(rank, world, port, q_out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_direct_ring_schedule_over_gloo(world):
+@pytest.mark.parametrize("world,window,plan", [(2, 0, False), (3, 0, False), (3, 10, True), (2, 5, True)])
+def test_direct_ring_schedule_over_gloo(world, window, plan):
+    """Without a plan every step runs; with one, the transfers and block updates of the pairs the
+    window mask empties are left out, each end deciding from the same matrix."""
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
-    port = 29600 + world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out)) for r in range(world)]
+    port = 29600 + world + 10 * int(plan) + (window % 7)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out, window, plan)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q_out.get(timeout=180) for _ in range(world)]
