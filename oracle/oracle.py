@@ -7,17 +7,21 @@ baseline can be timed.  Nothing in the product path may import it: only the test
 suite, the smoke check and the benchmark's cpu-baseline / reference arm do.
 
 Pinning.  The reference stores no golden arrays; its tests draw inputs from
-`jax.random` (which cannot be regenerated without JAX) and assert one property:
-ring attention equals dense softmax attention and its gradients
-(ring_attention/ring_test.py:26-42, :97-98, :165-171, :273-274, :298-300, :378).
-JAX is not installable here, so outputs of the reference itself cannot be
-produced: in the byte-for-byte sense this oracle is "parity unpinned".  What is
-pinned (tests/test_oracle.py): (1) the ring emulation below equals the dense
-restatement of the reference test's `mha` at every shape the reference tests use,
-to 1e-12 in float64; (2) the dense restatement equals torch's CPU
-scaled_dot_product_attention and torch autograd gradients, an independent
-implementation; (3) the NaN pattern of fully masked rows equals the dense
-softmax's (ring_test.py:273).
+`jax.random` and assert one property: ring attention equals dense softmax attention
+and its gradients (ring_attention/ring_test.py:26-42, :97-98, :165-171, :273-274,
+:298-300, :378).  JAX is not installable here, so the JAX/Pallas program itself cannot
+be run.  What pins this oracle:
+(1) the reference's own ring.py, imported unmodified and run on a NumPy stand-in for
+    the JAX names it uses (tests/golden/jax_on_numpy.py; `block_impl="jax"`, float64,
+    8 virtual devices): tests/test_reference_run.py holds this oracle to its out, L,
+    dQ, dK, dV at 1e-11, NaN and inf patterns included, and tests/golden/*.npz are
+    outputs of that run (tests/test_oracle.py::test_golden_fixtures);
+(2) the ring emulation below equals the dense restatement of the reference test's
+    `mha` at every shape the reference tests use, to 1e-12 in float64;
+(3) the dense restatement equals torch's CPU scaled_dot_product_attention and torch
+    autograd gradients, an independent implementation.
+Not pinned: the Pallas kernels of ring_kernel.py and XLA's float32 rounding (in that
+byte-for-byte sense: "parity unpinned").
 
 Each function cites the reference lines it follows.
 """
@@ -52,7 +56,9 @@ def mha(q, k, v, bias=None, sm_scale=None, dtype=np.float64, return_lse=False):
         a = p / l
         out = np.einsum("bhij,bjhd->bihd", a, v)
         if return_lse:
-            lse = (m + np.log(l))[..., 0]
+            # a row that sees no key: the ring carries m = -inf, l = 0 and ends with
+            # L = -inf + log 0 = -inf (ring.py:66-69, 135), while out = 0 / 0 = NaN
+            lse = np.where(np.isneginf(m), -np.inf, m + np.log(l))[..., 0]
             return out, lse
     return out
 

@@ -1,8 +1,12 @@
-"""Writes tests/golden/*.npz from the CPU oracle (oracle/oracle.py, float64).
+"""Writes tests/golden/*.npz: outputs of the REFERENCE's own code on seeded inputs.
 
-The reference project stores no golden arrays and cannot be run here (JAX is not
-installable), so these fixtures pin the ORACLE: they freeze today's float64 answers so
-that a later edit of the oracle, or of the engine, that changes results is caught.
+The reference project stores no golden arrays, and JAX cannot be installed here.  Its ring.py
+is therefore run on a NumPy stand-in for the JAX names it uses (jax_on_numpy.py, reference_run.py:
+one thread per virtual device, float64); what executes is the reference's Python: the public
+entry points, the custom-VJP forward and backward scans, the block functions, the rotation and
+the mask builder (`block_impl="jax"`; the Pallas kernels are not run).  The fixtures hold those
+outputs in float32 and travel to machines without the reference checkout.  Where the checkout is
+absent this script falls back to the CPU oracle (`source` in each file says which it was).
 Inputs are not stored; `inputs(case)` below regenerates them from a seeded NumPy PCG64
 stream.  Run from the repository root:  python tests/golden/make_golden.py
 """
@@ -68,13 +72,33 @@ def answers(name):
     return {"out": out, "lse": lse, "dq": dq, "dk": dk, "dv": dv}
 
 
+def reference_answers(name):
+    """The same five arrays from the reference's own code (reference_run.py)."""
+    sys.path.insert(0, HERE)
+    import reference_run as R
+
+    seed, b, lq, lk, h, d, n, mask = CASES[name]
+    q, k, v, do, extra = inputs(name)
+    if mask in ("none", "segments"):  # the general entry point; independent ids for queries and keys
+        return R.reference_answers(q, k, v, do, n, q_seg=extra.get("q_seg"), kv_seg=extra.get("kv_seg"))
+    return R.reference_answers(q, k, v, do, n, q_seg=extra.get("q_seg"), kv_seg=extra.get("kv_seg"),
+                               q_pos=extra.get("q_pos"), kv_pos=extra.get("kv_pos"), causal=True,
+                               api="ring_self_attention")
+
+
 def main():
+    sys.path.insert(0, HERE)
+    import reference_run as R
+
+    from_reference = R.available()
     for name in CASES:
-        ans = answers(name)
+        ans = reference_answers(name) if from_reference else answers(name)
+        ans["source"] = np.array("reference ring.py on the NumPy stand-in" if from_reference else "oracle")
+        source = ans.pop("source")
         if name.startswith("config1"):  # keep the file small: every 16th row
             ans = {k2: (a[:, ::16] if k2 != "lse" else a[:, :, ::16]) for k2, a in ans.items()}
         path = os.path.join(HERE, name + ".npz")
-        np.savez_compressed(path, **{k2: a.astype(np.float32) for k2, a in ans.items()})
+        np.savez_compressed(path, source=source, **{k2: a.astype(np.float32) for k2, a in ans.items()})
         print(path, os.path.getsize(path))
 
 

@@ -149,16 +149,26 @@ def test_alibi_window_bias_and_pair_counts():
 
 @pytest.mark.parametrize("name", list(G.CASES))
 def test_golden_fixtures(name):
-    """The committed fixtures still equal what the oracle computes (float32 storage)."""
+    """The committed fixtures are outputs of the reference's own code (run on the NumPy stand-in,
+    see make_golden.py), stored in float32: the oracle must reproduce them, NaN and inf patterns
+    included, to float32 rounding."""
     import os
 
     data = np.load(os.path.join(os.path.dirname(G.__file__), name + ".npz"))
+    assert str(data["source"]).startswith("reference"), "regenerate the fixtures where the reference checkout exists"
     ans = G.answers(name)
     for key in ("out", "lse", "dq", "dk", "dv"):
         a = ans[key]
         if name.startswith("config1"):
             a = a[:, ::16] if key != "lse" else a[:, :, ::16]
-        np.testing.assert_allclose(data[key], a.astype(np.float32), rtol=0, atol=0, equal_nan=True)
+        want = data[key]
+        assert np.array_equal(np.isnan(a), np.isnan(want)), key
+        ok = ~np.isnan(want)
+        assert np.array_equal(np.isinf(a[ok]), np.isinf(want[ok])), key
+        fin = ok & np.isfinite(want)
+        if fin.any():  # (dK and dV of the random-segment case are NaN throughout, ring.py:146)
+            scale = max(1.0, float(np.abs(want[fin]).max()))
+            assert np.abs(a[fin] - want[fin]).max() <= 2e-7 * scale, key
 
 
 def test_config1_ring_emulation_four_ranks():

@@ -1,0 +1,109 @@
+"""The oracle against the reference's own code.
+
+JAX cannot be installed here, so the reference's ring.py is run on a NumPy stand-in for the
+handful of JAX names it uses (tests/golden/jax_on_numpy.py: one thread per virtual device,
+`ppermute` / `psum` at a barrier, `scan` as a loop, `custom_vjp` as a tape).  Everything else
+that executes is the reference's Python: `ring_attention`, `ring_self_attention`, the custom-VJP
+forward and backward scans, `_fwd_block` / `_bwd_block`, `_rotate_block` and the built-in mask
+builder, in float64.  Needs the reference checkout; skipped where it is absent.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+import reference_run as R  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.skipif(not R.available(), reason="the reference checkout is not on this machine")
+
+
+def _same(name, got, want, tol=1e-11):
+    assert got.shape == want.shape, (name, got.shape, want.shape)
+    assert np.array_equal(np.isnan(got), np.isnan(want)), f"{name}: NaN pattern differs"
+    ok = ~np.isnan(want)
+    assert np.array_equal(np.isinf(got[ok]), np.isinf(want[ok])), f"{name}: inf pattern differs"
+    fin = ok & np.isfinite(want)
+    err = np.abs(got[fin] - want[fin]).max() if fin.any() else 0.0
+    assert err <= tol, f"{name}: max abs difference {err:.3e}"
+
+
+def _compare(ans, q, k, v, do, bias):
+    out, lse = O.mha(q, k, v, bias, return_lse=True)
+    dq, dk, dv = O.mha_grads(q, k, v, do, bias)
+    for name, want in (("out", out), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _same(name, ans[name], want)
+
+
+# ring_test.py:49-52 and :105-110: (q_len, kv_len, heads, head dim), 8 devices, batch 2
+@pytest.mark.parametrize("lq,lk,h,d", [(24, 16, 1, 2), (128, 64, 4, 64), (64, 128, 2, 16), (8, 8, 1, 1)])
+def test_general_entry_point_plain_and_cross_attention(lq, lk, h, d):
+    rng = np.random.default_rng(lq + lk)
+    q, k, v, do = (rng.standard_normal((2, n, h, d)) for n in (lq, lk, lk, lq))
+    ans = R.reference_answers(q, k, v, do, 8)
+    _compare(ans, q, k, v, do, None)
+    # the oracle's own ring over 8 virtual ranks (its restatement of the schedule) against the same run
+    sh = lambda x: np.split(x, 8, axis=1)
+    out, res = O.ring_attention_fwd(sh(q), sh(k), sh(v))
+    _same("ring out", np.concatenate(out, axis=1), ans["out"])
+
+
+def test_general_entry_point_with_a_segment_bias_fn():
+    """Independent random ids for queries and keys (ring_test.py:203-208): some query rows see
+    no key at all, and the reference's NaN pattern must be reproduced."""
+    rng = np.random.default_rng(3)
+    b, lq, lk, h, d = 2, 128, 64, 4, 16
+    q, k, v, do = (rng.standard_normal((b, n, h, d)) for n in (lq, lk, lk, lq))
+    q_seg = rng.integers(0, lq // 5, (b, lq)).astype(np.int32)
+    kv_seg = rng.integers(0, lq // 5, (b, lk)).astype(np.int32)
+    ans = R.reference_answers(q, k, v, do, 8, q_seg=q_seg, kv_seg=kv_seg)
+    bias = O.score_mod_bias(b, h, q_segment_ids=q_seg, kv_segment_ids=kv_seg)
+    assert np.isnan(ans["out"]).any(), "this case is meant to have fully masked rows"
+    _compare(ans, q, k, v, do, bias)
+
+
+# (no mask at all is left out: the reference's mask builder then indexes a 0-d bias, ring.py:409)
+@pytest.mark.parametrize("causal,segments,prefix", [(True, False, False), (True, True, False), (False, True, False),
+                                                     (False, False, True), (False, True, True)])
+def test_self_attention_entry_point_and_its_mask_builder(causal, segments, prefix):
+    """ring_self_attention (ring.py:328-449) through the stand-in's shard_map: bidirectional,
+    block-sparse, causal and prefix-LM masks and their combinations (ring_test.py:323-350)."""
+    rng = np.random.default_rng(11)
+    b, l, h, d, n = 2, 64, 2, 8, 8
+    q, k, v, do = (rng.standard_normal((b, l, h, d)) for _ in range(4))
+    seg = np.sort(rng.integers(0, 5, (b, l)), axis=1).astype(np.int32) if segments else None
+    pos = np.broadcast_to(np.arange(l, dtype=np.int32), (b, l)).copy() if (causal or prefix) else None
+    pre = (np.arange(l)[None] < rng.integers(4, 40, (b, 1))) if prefix else None
+    ans = R.reference_answers(q, k, v, do, n, q_seg=seg, kv_seg=seg, q_pos=pos, kv_pos=pos, q_pre=pre, kv_pre=pre,
+                              causal=causal, api="ring_self_attention")
+    bias = O.score_mod_bias(b, h, q_positions=pos, kv_positions=pos, q_segment_ids=seg, kv_segment_ids=seg,
+                            q_prefix_mask=pre, kv_prefix_mask=pre, causal=causal)
+    _compare(ans, q, k, v, do, bias)
+
+
+def test_block_functions_directly():
+    """_fwd_block / _bwd_block (ring.py:58-76, 140-157) against the oracle's block math, with a
+    carried state and a bias that masks some rows entirely."""
+    ref = R.load_reference()
+    rng = np.random.default_rng(5)
+    b, h, lq, lk, d = 2, 3, 12, 20, 4
+    q, k, v, do = (rng.standard_normal(s) for s in ((b, h, lq, d), (b, h, lk, d), (b, h, lk, d), (b, h, lq, d)))
+    bias = np.where(rng.random((b, 1, lq, lk)) < 0.4, -np.inf, 0.0)
+    bias[:, :, 3] = -np.inf
+    o0 = rng.standard_normal((b, h, lq, d))
+    m0 = rng.standard_normal((b, h, lq))
+    m0[:, :, 5] = -np.inf
+    l0 = rng.random((b, h, lq)) + 0.5
+    got = ref._fwd_block(q, k, v, bias, o0, m0, l0, 0.37)
+    want = O.fwd_block(q, k, v, bias, o0, m0, l0, 0.37)
+    for name, g, w in zip(("o", "m", "l"), got, want):
+        _same(name, np.asarray(g), w)
+    L = rng.standard_normal((b, h, lq)) + 3
+    got = ref._bwd_block(q, k, v, bias, o0, L, do, 0.37)
+    want = O.bwd_block(q, k, v, bias, o0, L, do, 0.37)
+    for name, g, w in zip(("dq", "dk", "dv"), got, want):
+        _same(name, np.asarray(g), w)
