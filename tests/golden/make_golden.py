@@ -33,6 +33,7 @@ CASES = {
     "segments_128_64": (1, 2, 128, 64, 4, 64, 8, "segments"),
     "self_causal_seg_512": (2, 2, 512, 512, 4, 16, 8, "causal+segments"),
     "config1_causal_1024": (0, 1, 1024, 1024, 4, 64, 4, "causal"),
+    "self_prefix_seg_256": (4, 2, 256, 256, 2, 32, 8, "prefix+segments"),
 }
 
 
@@ -49,7 +50,10 @@ def inputs(name):
         extra["kv_seg"] = rng.integers(0, lq // 5, (b, lk)).astype(np.int32)
     if mask == "causal+segments":  # ring_test.py:347-350
         extra["q_seg"] = extra["kv_seg"] = rng.integers(0, 5, (b, lq)).astype(np.int32)
-    if "causal" in mask:
+    if mask == "prefix+segments":  # ring.py:399-406: bidirectional inside the prefix, causal after it
+        extra["q_seg"] = extra["kv_seg"] = np.sort(rng.integers(0, 3, (b, lq)), axis=1).astype(np.int32)
+        extra["q_pre"] = extra["kv_pre"] = np.arange(lq)[None] % 97 < rng.integers(8, 60, (b, 1))
+    if "causal" in mask or "prefix" in mask:
         extra["q_pos"] = np.broadcast_to(np.arange(lq, dtype=np.int32), (b, lq)).copy()
         extra["kv_pos"] = np.broadcast_to(np.arange(lk, dtype=np.int32), (b, lk)).copy()
     return q, k, v, do, extra
@@ -61,6 +65,7 @@ def dense_bias(name, extra):
         return None
     return O.score_mod_bias(b, h, q_positions=extra.get("q_pos"), kv_positions=extra.get("kv_pos"),
                             q_segment_ids=extra.get("q_seg"), kv_segment_ids=extra.get("kv_seg"),
+                            q_prefix_mask=extra.get("q_pre"), kv_prefix_mask=extra.get("kv_pre"),
                             causal="causal" in mask)
 
 
@@ -82,8 +87,8 @@ def reference_answers(name):
     if mask in ("none", "segments"):  # the general entry point; independent ids for queries and keys
         return R.reference_answers(q, k, v, do, n, q_seg=extra.get("q_seg"), kv_seg=extra.get("kv_seg"))
     return R.reference_answers(q, k, v, do, n, q_seg=extra.get("q_seg"), kv_seg=extra.get("kv_seg"),
-                               q_pos=extra.get("q_pos"), kv_pos=extra.get("kv_pos"), causal=True,
-                               api="ring_self_attention")
+                               q_pos=extra.get("q_pos"), kv_pos=extra.get("kv_pos"), q_pre=extra.get("q_pre"),
+                               kv_pre=extra.get("kv_pre"), causal="causal" in mask, api="ring_self_attention")
 
 
 def main():

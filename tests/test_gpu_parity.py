@@ -214,9 +214,11 @@ def test_golden_fixtures(name):
     if mask != "none":
         sm = ra().ScoreMod(causal="causal" in mask)
         qkw = {"q_positions": T(extra["q_pos"]) if "q_pos" in extra else None,
-               "q_segment_ids": T(extra["q_seg"]) if "q_seg" in extra else None}
+               "q_segment_ids": T(extra["q_seg"]) if "q_seg" in extra else None,
+               "q_prefix_mask": to_dev(extra["q_pre"], torch.bool) if "q_pre" in extra else None}
         kkw = {"kv_positions": T(extra["kv_pos"]) if "kv_pos" in extra else None,
-               "kv_segment_ids": T(extra["kv_seg"]) if "kv_seg" in extra else None}
+               "kv_segment_ids": T(extra["kv_seg"]) if "kv_seg" in extra else None,
+               "kv_prefix_mask": to_dev(extra["kv_pre"], torch.bool) if "kv_pre" in extra else None}
     tq, tk, tv, tdo = (to_dev(x) for x in (q, k, v, do))
     out, dq, dk, dv = _grads(lambda a, b_, c: ra().ring_attention(a, b_, c, "sp", bias_fn=sm, bias_q_kwargs=qkw,
                                                                  bias_kv_kwargs=kkw, block_impl="simt"), tq, tk, tv, tdo)
