@@ -11,16 +11,17 @@ Pinning.  The reference stores no golden arrays; its tests draw inputs from
 and its gradients (ring_attention/ring_test.py:26-42, :97-98, :165-171, :273-274,
 :298-300, :378).  JAX is not installable here, so the JAX/Pallas program itself cannot
 be run.  What pins this oracle:
-(1) the reference's own ring.py, imported unmodified and run on a NumPy stand-in for
-    the JAX names it uses (tests/golden/jax_on_numpy.py; `block_impl="jax"`, float64,
-    8 virtual devices): tests/test_reference_run.py holds this oracle to its out, L,
-    dQ, dK, dV at 1e-11, NaN and inf patterns included, and tests/golden/*.npz are
+(1) the reference's own ring.py and ring_kernel.py, imported unmodified and run on a
+    NumPy stand-in for the JAX and Pallas names they use (tests/golden/jax_on_numpy.py;
+    8 virtual devices): tests/test_reference_run.py holds this oracle to their out, L,
+    dQ, dK, dV, NaN and inf patterns included, at 1e-11 for `block_impl="jax"` in
+    float64 and to float32 rounding for the Pallas kernels, and tests/golden/*.npz are
     outputs of that run (tests/test_oracle.py::test_golden_fixtures);
 (2) the ring emulation below equals the dense restatement of the reference test's
     `mha` at every shape the reference tests use, to 1e-12 in float64;
 (3) the dense restatement equals torch's CPU scaled_dot_product_attention and torch
     autograd gradients, an independent implementation.
-Not pinned: the Pallas kernels of ring_kernel.py and XLA's float32 rounding (in that
+Not pinned: XLA's / Triton's own float32 rounding and Pallas' real runtime (in that
 byte-for-byte sense: "parity unpinned").
 
 Each function cites the reference lines it follows.

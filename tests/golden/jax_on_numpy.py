@@ -13,8 +13,11 @@ What it provides, and nothing more:
   residuals on the calling rank's tape; `vjp_of_last_call(cotangent)` runs its backward rule;
 * `jax.experimental.shard_map.shard_map`, `jax.sharding.PartitionSpec` / `Mesh`: split the
   arguments along the named axis, run one thread per shard, concatenate the results;
-* placeholders for `jax.experimental.pallas` and `jaxtyping` so that the imports succeed (the
-  Pallas kernels of ring_kernel.py are NOT run: only `block_impl="jax"` works).
+* `jax.experimental.pallas`: an interpreter for the calls ring_kernel.py makes (`pallas_call`
+  over a grid with `BlockSpec` blocks, `program_id`, `dslice`, `load`, `dot`, `atomic_add`,
+  `cdiv`; `lax.fori_loop`; `ShapeDtypeStruct`): every grid point runs the kernel function on
+  views of the operands, one after the other, which is what Pallas' own interpret mode does;
+* a placeholder `jaxtyping` so that the imports succeed.
 
 `install()` puts these modules into `sys.modules`; import the reference after it.
 """
@@ -230,6 +233,92 @@ def shard_map(fn, mesh, in_specs, out_specs, check_rep=True):
     return run
 
 
+# ----------------------------------------------------------------------------- pallas
+class _Ref:
+    """A block of an operand as the kernel sees it: `ref[...]`, `ref.shape`, `pl.load(ref, idx)`."""
+
+    def __init__(self, view):
+        self.view = view
+
+    shape = property(lambda self: self.view.shape)
+    dtype = property(lambda self: self.view.dtype)
+
+    def __getitem__(self, idx):
+        return _f(np.array(self.view[idx], copy=True))
+
+    def __setitem__(self, idx, value):
+        self.view[idx] = value
+
+
+class BlockSpec:
+    def __init__(self, block_shape, index_map):
+        self.block_shape, self.index_map = tuple(block_shape), index_map
+
+
+class ShapeDtypeStruct:
+    def __init__(self, shape, dtype):
+        self.shape, self.dtype = tuple(shape), dtype
+
+
+_grid_index = threading.local()
+
+
+def _program_id(axis):
+    return _grid_index.value[axis]
+
+
+def _dslice(start, size=None):
+    return slice(0, start) if size is None else slice(start, start + size)
+
+
+def _block_view(array, spec, index):
+    """The block a BlockSpec selects at one grid point.  A block index past the end is clamped
+    so that the block stays inside the array, as lax.dynamic_slice (and with it Pallas'
+    interpret mode) does."""
+    where = spec.index_map(*index)
+    idx = []
+    for dim, (size, i) in enumerate(zip(spec.block_shape, where)):
+        if size is None:  # a squeezed dimension is a block of one row, clamped like the others
+            idx.append(min(int(i), array.shape[dim] - 1))  # (a [b, 1, lq, lk] bias serves every head)
+        else:
+            start = min(int(i) * size, max(array.shape[dim] - size, 0))
+            idx.append(slice(start, start + size))
+    return array[tuple(idx)]
+
+
+def _pallas_call(kernel, grid, in_specs, out_specs, out_shape, input_output_aliases=None, **unused):
+    single = not isinstance(out_shape, (list, tuple))
+    out_shapes = [out_shape] if single else list(out_shape)
+    out_specs_l = [out_specs] if single else list(out_specs)
+
+    def run(*args):
+        args = [None if a is None else np.asarray(a) for a in args]
+        outs = [np.zeros(s.shape, s.dtype) for s in out_shapes]
+        present = [a for a in args if a is not None]  # alias indices count the operands that exist
+        for src, dst in (input_output_aliases or {}).items():
+            outs[dst] = np.array(present[src], dtype=out_shapes[dst].dtype, copy=True)
+        for index in np.ndindex(*grid):
+            _grid_index.value = index
+            refs = [None if a is None else _Ref(_block_view(a, s, index)) for a, s in zip(args, in_specs)]
+            refs += [_Ref(_block_view(o, s, index)) for o, s in zip(outs, out_specs_l)]
+            kernel(*refs)
+        outs = [_f(o) for o in outs]
+        return outs[0] if single else outs
+
+    return run
+
+
+def _fori_loop(lower, upper, body, init):
+    carry = init
+    for i in range(int(lower), int(upper)):
+        carry = body(i, carry)
+    return carry
+
+
+def _atomic_add(ref, idx, value):
+    ref.view[idx] += np.asarray(value).astype(ref.view.dtype)
+
+
 # ----------------------------------------------------------------------------- install
 class _Subscript:
     def __getitem__(self, item):
@@ -243,17 +332,23 @@ def install():
     jax._numpy_standin = True
     jnp = _NumpyModule("jax.numpy")
     lax = types.ModuleType("jax.lax")
-    lax.scan, lax.psum, lax.ppermute = _scan, _psum, _ppermute
+    lax.scan, lax.psum, lax.ppermute, lax.fori_loop = _scan, _psum, _ppermute, _fori_loop
     sharding = types.ModuleType("jax.sharding")
     sharding.PartitionSpec, sharding.Mesh = PartitionSpec, Mesh
     experimental = types.ModuleType("jax.experimental")
     sm = types.ModuleType("jax.experimental.shard_map")
     sm.shard_map = shard_map
     pallas = types.ModuleType("jax.experimental.pallas")
+    pallas.program_id, pallas.dslice, pallas.ds = _program_id, _dslice, _dslice
+    pallas.load = lambda ref, idx: ref[idx]
+    pallas.dot = lambda a, b: _f(np.asarray(a) @ np.asarray(b))
+    pallas.cdiv = lambda a, b: -(-a // b)
+    pallas.atomic_add, pallas.BlockSpec, pallas.pallas_call = _atomic_add, BlockSpec, _pallas_call
     experimental.shard_map, experimental.pallas = sm, pallas
     jax.numpy, jax.lax, jax.sharding, jax.experimental = jnp, lax, sharding, experimental
     jax.custom_vjp = _CustomVjp
     jax.Array = np.ndarray
+    jax.ShapeDtypeStruct = ShapeDtypeStruct
     jaxtyping = types.ModuleType("jaxtyping")
     for name in ("Float", "Int", "Bool", "PyTree"):
         setattr(jaxtyping, name, _Subscript())

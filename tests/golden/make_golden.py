@@ -4,7 +4,7 @@ The reference project stores no golden arrays, and JAX cannot be installed here.
 is therefore run on a NumPy stand-in for the JAX names it uses (jax_on_numpy.py, reference_run.py:
 one thread per virtual device, float64); what executes is the reference's Python: the public
 entry points, the custom-VJP forward and backward scans, the block functions, the rotation and
-the mask builder (`block_impl="jax"`; the Pallas kernels are not run).  The fixtures hold those
+the mask builder (`block_impl="jax"`; tests/test_reference_run.py also runs the Pallas kernels).  The fixtures hold those
 outputs in float32 and travel to machines without the reference checkout.  Where the checkout is
 absent this script falls back to the CPU oracle (`source` in each file says which it was).
 Inputs are not stored; `inputs(case)` below regenerates them from a seeded NumPy PCG64

@@ -4,7 +4,8 @@ NumPy stand-in of jax_on_numpy.py, with one thread per virtual device, in float6
 `reference_answers(...)` returns out, L and the gradients of sum(out * do) for one case, computed
 by the reference's functions themselves: `ring_attention` / `ring_self_attention`, the custom-VJP
 pair `_ring_attention_fwd` / `_ring_attention_bwd`, `_fwd_block` / `_bwd_block`, `_rotate_block`
-and the built-in mask builder.  The Pallas kernels are not run.  Needs the reference checkout
+and the built-in mask builder; with `block_impl="pallas"` also the kernels of ring_kernel.py,
+through the stand-in's interpreter of the Pallas calls they make.  Needs the reference checkout
 (REFERENCE_DIR, default /root/reference); nothing here ships with the product.
 """
 from __future__ import annotations
@@ -35,22 +36,21 @@ def load_reference():
     return importlib.import_module("ring_attention.ring")
 
 
-def _f64(x):
-    return None if x is None else np.asarray(x, dtype=np.float64)
-
-
 def reference_answers(q, k, v, do, nranks, *, q_seg=None, kv_seg=None, q_pos=None, kv_pos=None,
-                      q_pre=None, kv_pre=None, causal=False, api="ring_attention"):
+                      q_pre=None, kv_pre=None, causal=False, api="ring_attention", block_impl="jax",
+                      dtype=np.float64):
     """q [b, lq, h, dk], k, v [b, lk, h, d], do like out; integer / bool arrays [b, l].
 
     api="ring_attention": the general entry point with a segment-id `bias_fn` written like the
     reference's own test helper (a pair is visible when the ids are equal); cross attention allowed.
     api="ring_self_attention": the full-service entry point with its built-in mask (segments,
     causal by positions, prefix-LM); q, k, v must have one length.
+    block_impl="pallas" runs the kernels of ring_kernel.py through the stand-in's Pallas
+    interpreter (tiles of min(length, 128) rows, ring.py:299-308); they carry m and l in float32.
     """
     ref = load_reference()
     jnp = sys.modules["jax.numpy"]
-    q, k, v, do = _f64(q), _f64(k), _f64(v), _f64(do)
+    q, k, v, do = (np.asarray(x, dtype=dtype) for x in (q, k, v, do))
     spec = standin.PartitionSpec(None, "sp")
     mesh = standin.Mesh(nranks)
 
@@ -68,7 +68,7 @@ def reference_answers(q, k, v, do, nranks, *, q_seg=None, kv_seg=None, q_pos=Non
 
         def program(qs, ks, vs, dos, qkw, kkw):
             out = ref.ring_attention(qs, ks, vs, axis_name="sp", bias_fn=bias_fn, bias_q_kwargs=qkw,
-                                     bias_kv_kwargs=kkw, block_impl="jax")
+                                     bias_kv_kwargs=kkw, block_impl=block_impl)
             return (out,) + tuple(tail(dos))
 
         qkw = {} if q_seg is None else {"q_segment_ids": q_seg}
@@ -78,7 +78,7 @@ def reference_answers(q, k, v, do, nranks, *, q_seg=None, kv_seg=None, q_pos=Non
     else:
         assert q_seg is kv_seg or np.array_equal(q_seg, kv_seg), "self attention: one set of segment ids"
         out = ref.ring_self_attention(q, k, v, mesh, spec, causal=causal, segment_ids=q_seg, positions=q_pos,
-                                      prefix_mask=q_pre, block_impl="jax")
+                                      prefix_mask=q_pre, block_impl=block_impl)
         ctx = standin.LAST_CTX
         parts = standin.run_spmd(ctx, tail, [[np.array_split(do, nranks, axis=1)[r]] for r in range(nranks)])
         L, dq, dk, dv = (np.concatenate([p[i] for p in parts], axis=1) for i in range(4))

@@ -107,3 +107,48 @@ def test_block_functions_directly():
     want = O.bwd_block(q, k, v, bias, o0, L, do, 0.37)
     for name, g, w in zip(("dq", "dk", "dv"), got, want):
         _same(name, np.asarray(g), w)
+
+
+# ---- the Pallas kernels of ring_kernel.py, through the stand-in's interpreter of the Pallas calls
+# they make (float32, as the reference's own tests run them; m and l are float32 inside the kernels)
+def _compare32(ans, q, k, v, do, bias, tol=2e-5):
+    out, lse = O.mha(q, k, v, bias, return_lse=True)
+    dq, dk, dv = O.mha_grads(q, k, v, do, bias)
+    for name, want in (("out", out), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _same(name, ans[name].astype(np.float64), want, tol)
+
+
+@pytest.mark.parametrize("lq,lk,h,d", [(24, 16, 1, 2), (128, 64, 4, 64), (2048, 1024, 2, 16)])
+def test_pallas_kernels_plain_and_cross_attention(lq, lk, h, d):
+    """ring_test.py:49-52, 105-110 with block_impl="pallas": 3-row shards up to two query tiles
+    per device."""
+    rng = np.random.default_rng(lq)
+    q, k, v, do = (rng.standard_normal((2, n, h, d)).astype(np.float32) for n in (lq, lk, lk, lq))
+    ans = R.reference_answers(q, k, v, do, 8, block_impl="pallas", dtype=np.float32)
+    _compare32(ans, q, k, v, do, None)
+
+
+def test_pallas_kernels_with_the_built_in_mask_and_two_key_tiles_per_device():
+    """Causal + segments self attention, 256 tokens per device: two query tiles and two key
+    tiles per block call, the bias tile read through ring_kernel.py:253-256."""
+    rng = np.random.default_rng(21)
+    b, l, h, d, n = 1, 2048, 2, 16, 8
+    q, k, v, do = (rng.standard_normal((b, l, h, d)).astype(np.float32) for _ in range(4))
+    seg = np.sort(rng.integers(0, 5, (b, l)), axis=1).astype(np.int32)
+    pos = np.broadcast_to(np.arange(l, dtype=np.int32), (b, l)).copy()
+    ans = R.reference_answers(q, k, v, do, n, q_seg=seg, kv_seg=seg, q_pos=pos, kv_pos=pos, causal=True,
+                              api="ring_self_attention", block_impl="pallas", dtype=np.float32)
+    bias = O.score_mod_bias(b, h, q_positions=pos, kv_positions=pos, q_segment_ids=seg, kv_segment_ids=seg, causal=True)
+    _compare32(ans, q, k, v, do, bias)
+
+
+def test_pallas_kernels_with_a_segment_bias_fn_keep_the_nan_pattern():
+    rng = np.random.default_rng(3)
+    b, lq, lk, h, d = 2, 128, 64, 2, 16
+    q, k, v, do = (rng.standard_normal((b, n, h, d)).astype(np.float32) for n in (lq, lk, lk, lq))
+    q_seg = rng.integers(0, lq // 5, (b, lq)).astype(np.int32)
+    kv_seg = rng.integers(0, lq // 5, (b, lk)).astype(np.int32)
+    ans = R.reference_answers(q, k, v, do, 8, q_seg=q_seg, kv_seg=kv_seg, block_impl="pallas", dtype=np.float32)
+    bias = O.score_mod_bias(b, h, q_segment_ids=q_seg, kv_segment_ids=kv_seg)
+    assert np.isnan(ans["out"]).any()
+    _compare32(ans, q, k, v, do, bias)
