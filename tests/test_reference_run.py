@@ -152,3 +152,27 @@ def test_pallas_kernels_with_a_segment_bias_fn_keep_the_nan_pattern():
     bias = O.score_mod_bias(b, h, q_segment_ids=q_seg, kv_segment_ids=kv_seg)
     assert np.isnan(ans["out"]).any()
     _compare32(ans, q, k, v, do, bias)
+
+
+def test_zigzag_token_layout_is_legal_in_the_reference():
+    """The masks are driven by the position arrays (ring.py:396), not by block indices, so the
+    reference itself gives the same answer when every device holds chunks r and 2N-1-r of the
+    sequence (the load-balanced layout the benchmark uses) instead of one contiguous chunk."""
+    from ring_attention_b200.layout import zigzag_indices
+
+    rng = np.random.default_rng(8)
+    b, l, h, d, n = 2, 128, 2, 8, 4
+    q, k, v, do = (rng.standard_normal((b, l, h, d)) for _ in range(4))
+    seg = np.sort(rng.integers(0, 3, (b, l)), axis=1).astype(np.int32)
+    pos = np.broadcast_to(np.arange(l, dtype=np.int32), (b, l)).copy()
+    order = np.concatenate([zigzag_indices(l, r, n).numpy() for r in range(n)])  # device r's tokens, in rank order
+    take = lambda x: np.ascontiguousarray(x[:, order])
+    ans = R.reference_answers(take(q), take(k), take(v), take(do), n, q_seg=take(seg), kv_seg=take(seg),
+                              q_pos=take(pos), kv_pos=take(pos), causal=True, api="ring_self_attention")
+    bias = O.score_mod_bias(b, h, q_positions=pos, kv_positions=pos, q_segment_ids=seg, kv_segment_ids=seg, causal=True)
+    out, lse = O.mha(q, k, v, bias, return_lse=True)
+    dq, dk, dv = O.mha_grads(q, k, v, do, bias)
+    back = np.argsort(order)
+    for name, want in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _same(name, ans[name][:, back], want)
+    _same("lse", ans["lse"][:, :, back], lse)
