@@ -498,8 +498,9 @@ def ring_self_attention(
     positions: Optional[torch.Tensor] = None,
     prefix_mask: Optional[torch.Tensor] = None,
     block_impl: str = "cuda",
+    plan: Optional["RingPlan"] = None,
 ) -> torch.Tensor:
-    """Self-attention over this rank's shard: the signature of ring.py:328-340.
+    """Self-attention over this rank's shard: the signature of ring.py:328-340, plus `plan`.
 
     Arrays are the local shards ([b, l/N, ...]) of arrays partitioned as `pspec` over
     `mesh`; `pspec[1]` names the sequence axis (ring.py:432).  Supports bidirectional,
@@ -521,4 +522,4 @@ def ring_self_attention(
     ring = mesh.ring(axis) if mesh is not None else resolve_axis(axis)
     return ring_attention(q, k, v, axis_name=ring, sm_scale=sm_scale, bias_fn=bias_fn,
                           bias_q_kwargs=q_kw if needs_mod else None,
-                          bias_kv_kwargs=kv_kw if needs_mod else None, block_impl=block_impl)
+                          bias_kv_kwargs=kv_kw if needs_mod else None, block_impl=block_impl, plan=plan)
