@@ -176,3 +176,29 @@ def test_zigzag_token_layout_is_legal_in_the_reference():
     for name, want in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
         _same(name, ans[name][:, back], want)
     _same("lse", ans["lse"][:, :, back], lse)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_small_cases(seed):
+    """Seeded random shapes, device counts and mask combinations, both block implementations."""
+    rng = np.random.default_rng(1000 + seed)
+    n = int(rng.choice([2, 3, 4, 8]))
+    c = int(rng.choice([1, 3, 8, 16]))
+    b, h, d = int(rng.integers(1, 3)), int(rng.integers(1, 4)), int(rng.choice([1, 2, 8, 16]))
+    l = n * c
+    impl = "pallas" if seed % 2 else "jax"
+    dtype = np.float32 if impl == "pallas" else np.float64
+    q, k, v, do = (rng.standard_normal((b, l, h, d)).astype(dtype) for _ in range(4))
+    kind = seed % 4
+    causal = kind in (0, 1)
+    seg = np.sort(rng.integers(0, 3, (b, l)), axis=1).astype(np.int32) if kind in (1, 2, 3) else None
+    pre = (np.arange(l)[None] < rng.integers(1, l + 1, (b, 1))) if kind == 3 else None
+    pos = np.broadcast_to(np.arange(l, dtype=np.int32), (b, l)).copy() if (causal or pre is not None) else None
+    ans = R.reference_answers(q, k, v, do, n, q_seg=seg, kv_seg=seg, q_pos=pos, kv_pos=pos, q_pre=pre, kv_pre=pre,
+                              causal=causal, api="ring_self_attention", block_impl=impl, dtype=dtype)
+    bias = O.score_mod_bias(b, h, q_positions=pos, kv_positions=pos, q_segment_ids=seg, kv_segment_ids=seg,
+                            q_prefix_mask=pre, kv_prefix_mask=pre, causal=causal)
+    if impl == "pallas":
+        _compare32(ans, q, k, v, do, bias)
+    else:
+        _compare(ans, q, k, v, do, bias)
