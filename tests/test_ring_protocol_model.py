@@ -1,0 +1,285 @@
+"""A host-side model of the peer-copy ring protocol of csrc/ring.cu, run to completion under
+random interleavings.
+
+The CUDA schedule cannot run without GPUs, and at most 4 of them are ever available to the
+tests, so this file restates its ordering rules -- which stream an operation is enqueued on,
+which flag counter it waits for or publishes, which event ties two streams of a rank together,
+which buffer a copy overwrites -- and executes them for 2 to 8 ranks with every stream of every
+rank advancing in random order.  It checks that nothing deadlocks, that every block step reads
+the K/V block (or the dK/dV contribution) of the rank and step it should, and that no buffer is
+overwritten while its reader has not finished; with and without a plan that leaves out
+(query shard, K/V block) pairs, over several calls in a row (the flag counters carry over).
+
+Counters (one page per rank, written by peers): KV_READY[slot], PART_READY[slot],
+PROGRESS[rank], ADDED[rank]; `epoch` advances by the ring size per call.
+"""
+import random
+
+import pytest
+
+
+class Event:
+    def __init__(self):
+        self.enqueued = 0
+        self.done = 0
+
+
+class Rank:
+    def __init__(self, me, n):
+        self.me, self.n = me, n
+        self.flags = {}  # (name, index) -> value, this rank's page
+        self.stage = [None, None]  # K/V staging slots: (owner, step, call)
+        self.rpart = [None, None]  # received contributions: (giver, step, call)
+        self.part = [None, None]  # own contribution buffers: (step, call) being built / sent
+        self.streams = {"main": [], "push": [], "reduce": []}
+        self.events = {}
+        self.log = []
+
+    def flag(self, name, index):
+        return self.flags.get((name, index), 0)
+
+    def event(self, name):
+        return self.events.setdefault(name, Event())
+
+
+class Model:
+    def __init__(self, n, need):
+        self.n, self.need = n, need
+        self.ranks = [Rank(r, n) for r in range(n)]
+        self.epoch = 0
+        self.call = 0
+
+    # ---- enqueue helpers (host side, program order) -------------------------------------
+    def op(self, r, stream, fn, what):
+        self.ranks[r].streams[stream].append((fn, what))
+
+    def record(self, r, stream, name):
+        ev = self.ranks[r].event(name)
+        ev.enqueued += 1
+        ticket = ev.enqueued
+
+        def run():
+            ev.done = max(ev.done, ticket)
+            return True
+
+        self.op(r, stream, run, f"record {name}")
+
+    def wait_event(self, r, stream, name):
+        ev = self.ranks[r].event(name)
+        ticket = ev.enqueued  # the most recent record at the time of the call; none: no wait
+        self.op(r, stream, lambda: ev.done >= ticket, f"wait {name}")
+
+    def wait_flag(self, r, stream, name, index, target):
+        rk = self.ranks[r]
+        self.op(r, stream, lambda: rk.flag(name, index) >= target, f"wait {name}[{index}] >= {target}")
+
+    def set_flag(self, r, stream, peer, name, index, value):
+        targets = [j for j in range(self.n) if (j == peer if peer >= 0 else j != r)]
+
+        def run():
+            for j in targets:
+                key = (name, index)
+                assert self.ranks[j].flags.get(key, 0) <= value, f"counter {name}[{index}] of rank {j} went backwards"
+                self.ranks[j].flags[key] = value
+            return True
+
+        self.op(r, stream, run, f"set {name}[{index}] = {value} at {targets}")
+
+    def needed(self, q_rank, kv_rank):
+        return self.need is None or self.need[q_rank][kv_rank]
+
+    # ---- the schedule: mirrors send_kv / wait_kv / step_done / ra_ring_fwd / ra_ring_bwd ----
+    def send_kv(self, me, t):
+        n, E, slot, call = self.n, self.epoch, t & 1, self.call
+        to = (me + t) % n
+        if not self.needed(to, me):
+            return
+        self.wait_flag(me, "push", "PROGRESS", to, E + t - 1 if t >= 3 else E)
+
+        def copy():
+            old = self.ranks[to].stage[slot]
+            if old is not None:  # the slot's previous block must have been consumed
+                owner, step, c = old
+                assert ("done", owner, step, c) in self.ranks[to].log, f"rank {to} stage[{slot}] overwritten before use"
+            self.ranks[to].stage[slot] = (me, t, call)
+            return True
+
+        self.op(me, "push", copy, f"push K/V to {to} slot {slot}")
+        self.set_flag(me, "push", to, "KV_READY", slot, E + t)
+
+    def block(self, me, stream, t, kind):
+        n, call = self.n, self.call
+        src = (me - t) % n
+
+        def run():
+            rk = self.ranks[me]
+            if t > 0:
+                assert rk.stage[t & 1] == (src, t, call), f"rank {me} step {t} ({kind}) reads {rk.stage[t & 1]}, wants {(src, t, call)}"
+            rk.log.append(("block", kind, t, call))
+            return True
+
+        self.op(me, stream, run, f"{kind} block step {t}")
+
+    def step_done(self, me, t):
+        src, call = (me - t) % self.n, self.call
+
+        def run():
+            self.ranks[me].log.append(("done", src, t, call))
+            return True
+
+        self.op(me, "main", run, f"step {t} done")
+        self.set_flag(me, "main", -1, "PROGRESS", me, self.epoch + t + 1)
+
+    def begin_call(self, me):
+        self.record(me, "main", "ev_start")
+        self.wait_event(me, "push", "ev_start")
+        self.wait_event(me, "reduce", "ev_start")
+
+    def end_call(self, me):
+        self.record(me, "push", "ev_push_tail")
+        self.wait_event(me, "main", "ev_push_tail")
+
+    def forward(self):
+        n, E = self.n, self.epoch
+        for me in range(n):
+            self.begin_call(me)
+            for t in range(n):
+                if t + 1 < n:
+                    self.send_kv(me, t + 1)
+                if t > 0 and not self.needed(me, (me - t) % n):
+                    self.step_done(me, t)
+                    continue
+                if t > 0:
+                    self.wait_flag(me, "main", "KV_READY", t & 1, E + t)
+                self.block(me, "main", t, "fwd")
+                self.step_done(me, t)
+            self.set_flag(me, "main", -1, "ADDED", me, E + n)
+            self.end_call(me)
+        self.epoch += n
+        self.call += 1
+
+    def backward(self):
+        n, E, call = self.n, self.epoch, self.call
+        for me in range(n):
+            rk = self.ranks[me]
+            self.begin_call(me)
+            for t in range(n):
+                if t + 1 < n:
+                    self.send_kv(me, t + 1)
+                if t == 0:
+                    self.block(me, "main", 0, "bwd own part 1")
+                    self.step_done(me, 0)
+                    self.record(me, "main", "ev_step0")
+                    self.wait_event(me, "reduce", "ev_step0")
+                    continue
+                slot = t & 1
+                owner, giver = (me - t) % n, (me + t) % n
+                compute, receive = self.needed(me, owner), self.needed(giver, me)
+                if compute:
+                    self.wait_flag(me, "main", "KV_READY", slot, E + t)
+                    if t >= 3:
+                        self.wait_event(me, "main", f"ev_sent{slot}")
+
+                    def clear(slot=slot, t=t, rk=rk, me=me):
+                        old = rk.part[slot]
+                        assert old is None or old[2] == "sent", f"rank {me} part[{slot}] cleared while {old} is in flight"
+                        rk.part[slot] = (t, call, "built")
+                        return True
+
+                    self.op(me, "main", clear, f"clear part[{slot}]")
+                    self.block(me, "main", t, "bwd")
+                self.step_done(me, t)
+                if compute:
+                    self.record(me, "main", f"ev_part{slot}")
+                    self.wait_event(me, "push", f"ev_part{slot}")
+                    self.wait_flag(me, "push", "ADDED", owner, E + t - 1 if t >= 3 else E)
+
+                    def give(slot=slot, t=t, owner=owner, rk=rk, me=me):
+                        assert rk.part[slot] == (t, call, "built"), (me, rk.part[slot])
+                        old = self.ranks[owner].rpart[slot]
+                        assert old is None or old[3] == "added", f"rank {owner} rpart[{slot}] overwritten while {old} is unread"
+                        self.ranks[owner].rpart[slot] = (me, t, call, "fresh")
+                        rk.part[slot] = (t, call, "sent")
+                        return True
+
+                    self.op(me, "push", give, f"push contribution to {owner}")
+                    self.set_flag(me, "push", owner, "PART_READY", slot, E + t)
+                    self.record(me, "push", f"ev_sent{slot}")
+                if receive:
+                    self.wait_flag(me, "reduce", "PART_READY", slot, E + t)
+
+                    def add(slot=slot, t=t, giver=giver, rk=rk, me=me):
+                        assert rk.rpart[slot] == (giver, t, call, "fresh"), f"rank {me} adds {rk.rpart[slot]}, wants {(giver, t, call)}"
+                        rk.rpart[slot] = (giver, t, call, "added")
+                        rk.log.append(("added", giver, t, call))
+                        return True
+
+                    self.op(me, "reduce", add, f"add contribution of {giver}")
+                self.set_flag(me, "reduce", -1, "ADDED", me, E + t + 1)
+            self.record(me, "reduce", "ev_tail")
+            self.block(me, "main", 0, "bwd own part 2")
+            self.wait_event(me, "main", "ev_tail")
+            self.op(me, "main", lambda me=me: self.ranks[me].log.append(("finished", call)) or True, "casts")
+            self.end_call(me)
+        self.epoch += n
+        self.call += 1
+
+    # ---- execution: any stream whose head operation can run, in random order ------------------
+    def run(self, rng):
+        heads = [(r, s) for r in range(self.n) for s in ("main", "push", "reduce")]
+        pos = {h: 0 for h in heads}
+        while True:
+            rng.shuffle(heads)
+            progressed, left = False, 0
+            for h in heads:
+                ops = self.ranks[h[0]].streams[h[1]]
+                burst = rng.randint(1, 4)
+                while pos[h] < len(ops) and burst > 0:
+                    fn, _ = ops[pos[h]]
+                    if not fn():
+                        break
+                    pos[h] += 1
+                    burst -= 1
+                    progressed = True
+                left += len(ops) - pos[h]
+            if left == 0:
+                return
+            if not progressed:
+                stuck = {h: self.ranks[h[0]].streams[h[1]][pos[h]][1] for h in heads
+                         if pos[h] < len(self.ranks[h[0]].streams[h[1]])}
+                raise AssertionError(f"deadlock: {stuck}")
+
+
+def _random_plan(n, rng, density):
+    need = [[r == o or rng.random() < density for o in range(n)] for r in range(n)]
+    return need
+
+
+def _check(model, n, calls):
+    for r in range(n):
+        log = model.ranks[r].log
+        for call, kind in enumerate(calls):
+            want = [t for t in range(n) if t == 0 or model.needed(r, (r - t) % n)]
+            got = [e[2] for e in log if e[0] == "block" and e[3] == call and e[1] in ("fwd", "bwd")]
+            if kind == "fwd":
+                assert got == want, (r, call, got, want)
+            else:
+                assert got == want[1:], (r, call, got, want)
+                givers = sorted(e[1] for e in log if e[0] == "added" and e[3] == call)
+                assert givers == sorted((r + t) % n for t in range(1, n) if model.needed((r + t) % n, r)), (r, call, givers)
+                assert ("finished", call) in log
+
+
+@pytest.mark.parametrize("n", [2, 3, 4, 5, 8])
+@pytest.mark.parametrize("plan", ["none", "dense", "sparse", "diagonal"])
+def test_protocol_runs_to_completion_under_random_interleavings(n, plan):
+    calls = ["fwd", "bwd", "fwd", "fwd", "bwd", "bwd"]
+    for seed in range(6):
+        rng = random.Random(1000 * n + seed)
+        need = {"none": None, "dense": _random_plan(n, rng, 0.8), "sparse": _random_plan(n, rng, 0.3),
+                "diagonal": _random_plan(n, rng, 0.0)}[plan]
+        model = Model(n, need)
+        for kind in calls:  # the host enqueues whole calls without waiting for the device
+            model.forward() if kind == "fwd" else model.backward()
+        model.run(rng)
+        _check(model, n, calls)
