@@ -155,16 +155,16 @@ struct FlagList {
   int n;
 };
 
-// One thread; waits until *flag >= target.  Bounded: gives up after about two seconds of
-// cycles, records it in the status word and returns, so the stream always drains.
-__global__ void wait_flag_kernel(const uint64_t* flag, uint64_t target, unsigned int* status) {
+// One thread; waits until *flag >= target.  Bounded: gives up after max_cycles SM cycles,
+// records it in the status word and returns, so the stream always drains.
+__global__ void wait_flag_kernel(const uint64_t* flag, uint64_t target, unsigned int* status, long long max_cycles) {
   const long long t0 = clock64();
   while (true) {
     uint64_t v;
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
     if (v >= target) return;
     __nanosleep(100);
-    if (clock64() - t0 > 4000000000LL) {
+    if (clock64() - t0 > max_cycles) {
       atomicOr(status, kStRingWait);
       return;
     }
@@ -376,7 +376,16 @@ int block_mark(ra_ring_t* r, int dir, cudaStream_t s) {
 int launch_wait(ra_ring_t* r, cudaStream_t s, int flag_index, uint64_t target) {
   unsigned int* status = device_status_word();
   if (!status) return fail(RA_ERR_CUDA, "status word symbol not found");
-  wait_flag_kernel<<<1, 1, 0, s>>>(r->flags + flag_index, target, status);
+  // How long a rank waits for a peer before it gives up (the peer may simply be late: another
+  // stream of work, a slow host).  RA_RING_WAIT_MS, default 10 s; counted in SM cycles at 2 GHz.
+  static const long long max_cycles = [] {
+    const char* env = getenv("RA_RING_WAIT_MS");
+    long long ms = env ? atoll(env) : 10000;
+    if (ms < 1) ms = 1;
+    if (ms > 600000) ms = 600000;
+    return ms * 2000000LL;
+  }();
+  wait_flag_kernel<<<1, 1, 0, s>>>(r->flags + flag_index, target, status, max_cycles);
   count_launch();
   RA_CUDA(cudaGetLastError(), "wait_flag_kernel");
   return 0;
