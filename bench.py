@@ -155,28 +155,57 @@ class ClockSampler:
                 "samples": len(s)}
 
 
+def host_threads():
+    """Cores this process may use (its affinity mask), which is what the BLAS pool is set to."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(w, nranks=4, budget_s=20.0):
     """The reference's algorithm (ring.py:79-211) on the host cores through the oracle port:
     a bounded sample of the workload (one batch element, a few heads, a shorter sequence),
-    converted to the metric's unit through the exact FLOP count."""
+    converted to the metric's unit through the exact FLOP count.  The BLAS thread count is
+    set explicitly (a launcher may have exported OMP_NUM_THREADS=1) and the count in use is
+    what the line reports."""
+    from threadpoolctl import threadpool_info, threadpool_limits
+
     from oracle import oracle as O
 
-    cores = os.cpu_count() or 1
-    s, heads = 4096, 4
-    sample_flops = O.causal_flops(1, heads, s, w["d"])
-    t = O.timed_cpu_ring_causal(1, heads, s, w["d"], nranks)  # warm-up + size probe
-    reps = max(1, min(8, int(budget_s / max(t, 1e-3)) - 1))
-    ts = [O.timed_cpu_ring_causal(1, heads, s, w["d"], nranks, seed=i + 1) for i in range(reps)]
+    want = host_threads()
+    with threadpool_limits(limits=want):
+        used = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+        s, heads = 4096, 4
+        sample_flops = O.causal_flops(1, heads, s, w["d"])
+        t = O.timed_cpu_ring_causal(1, heads, s, w["d"], nranks)  # warm-up + size probe
+        reps = max(1, min(8, int(budget_s / max(t, 1e-3)) - 1))
+        ts = [O.timed_cpu_ring_causal(1, heads, s, w["d"], nranks, seed=i + 1) for i in range(reps)]
     best = min(ts + [t])
     flops_per_s = sample_flops / best
     tokens_per_s = w["b"] * w["s"] / (flops(w) / flops_per_s)
     return {
-        "value": tokens_per_s, "unit": "tokens/s", "cores": cores, "kind": "port",
-        "sample": f"oracle port (NumPy float32, BLAS on {cores} threads), causal fwd+bwd, b=1 h={heads} "
+        "value": tokens_per_s, "unit": "tokens/s", "cores": used, "kind": "port",
+        "sample": f"oracle port (NumPy float32, BLAS on {used} threads), causal fwd+bwd, b=1 h={heads} "
                   f"S={s} d={w['d']} over {nranks} virtual ranks, best of {len(ts) + 1}: {best:.3f} s = "
                   f"{flops_per_s / 1e9:.1f} GFLOP/s; scaled to the workload by its exact FLOP count",
-        "gflops": flops_per_s / 1e9,
+        "gflops": flops_per_s / 1e9, "extrapolated": True, "sample_seconds": best, "sample_tokens": s,
     }
+
+
+def cpu_config1():
+    """BASELINE.json's CPU-runnable configuration, timed for real (nothing extrapolated):
+    fp32 causal forward + backward, batch 1, 4 heads, 1024 tokens over 4 virtual ranks, head dim 64."""
+    from threadpoolctl import threadpool_limits
+
+    from oracle import oracle as O
+
+    with threadpool_limits(limits=host_threads()):
+        O.timed_cpu_ring_causal(1, 4, 1024, 64, 4)
+        ts = [O.timed_cpu_ring_causal(1, 4, 1024, 64, 4, seed=i + 1) for i in range(5)]
+    best = min(ts)
+    return {"workload": "config1: fp32 causal fwd+bwd, b1 h4 S1024 d64, 4 virtual ranks", "seconds": best,
+            "tokens_per_s": 1024 / best, "gflops": O.causal_flops(1, 4, 1024, 64) / best / 1e9, "extrapolated": False}
 
 
 def run_reference(args, w):
@@ -200,11 +229,115 @@ def run_reference(args, w):
         "config": workload_config(args, w, args.gpus),
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "extrapolated": True, "sample_seconds": base["sample_seconds"],
+        "config1_cpu": cpu_config1(),
         "note": "reference JAX path unavailable on this box (jax not installed, no network); "
-                "this is the CPU restatement of its algorithm; ms_per_step is the workload's time "
-                "extrapolated from the sample by FLOP count",
+                "this is the CPU restatement of its algorithm; every step times a bounded sample "
+                "(sample_seconds, measured) and ms_per_step is the workload's time extrapolated from it by "
+                "FLOP count, so it does not fit inside this run; config1_cpu is BASELINE.json's CPU-runnable "
+                "configuration timed for real",
     }
     print(json.dumps(line), flush=True)
+
+
+def shard_slice(r, t, head, b, c, d, std, dt):
+    """Tensor t (0 q, 1 k, 2 v, 3 dO) of rank r's shard, one head: [b, c, d].  Every (rank, tensor,
+    head) has a seed of its own, so that any rank can rebuild one head of the whole sequence on
+    the host for the parity check without drawing everything."""
+    import torch
+
+    g = torch.Generator().manual_seed(1234 + (r * 4 + t) * 4096 + head)
+    return (torch.randn((b, c, d), generator=g) * std).to(dt)
+
+
+def shard_indices(layout, total, r, n):
+    """Global token index (= position) of every local token of rank r."""
+    import torch
+
+    if layout == "zigzag" and n > 1:
+        from ring_attention_b200 import zigzag_indices
+
+        return zigzag_indices(total, r, n)
+    c = total // n
+    return torch.arange(c) + r * c
+
+
+def bind_to_gpu_numa(local):
+    """Runs this process on the CPUs of the NUMA node its GPU hangs off, so that the pinned host
+    buffers allocated afterwards are local to the GPU's PCIe root.  Returns what was found."""
+    import torch
+
+    info = {"numa_node": None, "cpus": host_threads()}
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        path = f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        info["numa_node"] = node
+        if node >= 0:
+            cpus = set()
+            for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            cpus &= os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+                info["cpus"] = len(cpus)
+    except Exception as e:  # sysfs layout differs, no permission: measure as is
+        info["note"] = f"not bound: {type(e).__name__}"
+    return info
+
+
+def parity_check(w, args, rank, N, results, seg_global, slopes, backward):
+    """Sampled rows of this rank's results against the CPU oracle on the whole sequence.
+
+    One (batch, head) per rank: the other ranks' shards of that head are rebuilt from their
+    seeds, ~16 query rows of this rank's shard give out, L and dQ, and up to 8 of its key rows
+    give dK, dV (only key rows whose gradient the oracle can afford: a key at position p of a
+    causal sequence needs L and delta of every later query).  Bound: 2e-2 abs + 1e-2 rel."""
+    import numpy as np
+    import torch
+    from threadpoolctl import threadpool_limits
+
+    from oracle import oracle as O
+
+    b, h, d, S = w["b"], w["h"], w["d"], w["s"]
+    c = S // N
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    bb, hh = b - 1, (rank * 5 + 3) % h
+    G = [np.zeros((S, d)) for _ in range(4)]
+    for r in range(N):
+        idx_r = shard_indices(args.layout, S, r, N).numpy()
+        for t in range(4 if backward else 3):
+            G[t][idx_r] = shard_slice(r, t, hh, b, c, d, w.get("std", 1.0), dt)[bb].to(torch.float64).numpy()
+    idx = shard_indices(args.layout, S, rank, N).numpy()
+    rng = np.random.default_rng(99 + rank)
+    q_loc = np.unique(np.concatenate([[0, c - 1], rng.integers(0, c, 14)]))
+    k_loc = np.array([], np.int64)
+    if backward:
+        if seg_global is not None:
+            ok = np.ones(c, bool)  # a key is seen inside its document only
+        else:
+            p = idx.astype(np.float64)
+            ok = (float(S) ** 2 - p ** 2) / 2 * 4 * d <= 3e11
+        cand = np.nonzero(ok)[0]
+        if cand.size:
+            k_loc = np.unique(rng.choice(cand, size=min(8, cand.size), replace=False))
+    scale = 1 / math.sqrt(d)
+    with threadpool_limits(limits=max(1, host_threads() // N)):
+        want = O.sampled_rows(G[0], G[1], G[2], G[3], scale, idx[q_loc], idx[k_loc], seg=seg_global,
+                              window=w.get("window", 0), slope=None if slopes is None else float(slopes[hh]),
+                              causal=True, score_dtype=np.float32)
+    f = lambda t: t.detach().to(torch.float64).cpu().numpy()
+    excess = {"out": O.bf16_excess(f(results["out"][bb, q_loc, hh]), want["out"]),
+              "L": O.bf16_excess(f(results["lse"][bb, hh, q_loc]), want["L"])}
+    if backward:
+        excess["dq"] = O.bf16_excess(f(results["dq"][bb, q_loc, hh]), want["dq"])
+        if k_loc.size:
+            excess["dk"] = O.bf16_excess(f(results["dk"][bb, k_loc, hh]), want["dk"])
+            excess["dv"] = O.bf16_excess(f(results["dv"][bb, k_loc, hh]), want["dv"])
+    worst = max(excess.values())
+    return {"ok": bool(worst <= 0 and all(np.isfinite(v) for v in excess.values())), "max_excess": worst,
+            "rows": int(q_loc.size), "key_rows": int(k_loc.size), "head": [int(bb), int(hh)], "excess": excess}
 
 
 def workload_config(args, w, n):
@@ -256,6 +389,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
     torch.cuda.set_device(local)
+    host_info = bind_to_gpu_numa(local)  # before any pinned allocation
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     mesh = ra.Mesh((1, world), ("dp", "sp"))
@@ -269,20 +403,17 @@ def main():
     check(lib.ra_set_impl({"cuda": 0, "simt": 1, "tcgen05": 2}[args.block_impl]))
 
     # synthetic inputs, pinned on the host (e2e) and resident on the device (value)
-    g = torch.Generator().manual_seed(1234 + rank)
-    host = [(torch.randn((b, c, h, d), generator=g) * w.get("std", 1.0)).to(dt).pin_memory() for _ in range(4)]
+    host = [torch.stack([shard_slice(rank, t, hd, b, c, d, w.get("std", 1.0), dt) for hd in range(h)], dim=2).pin_memory()
+            for t in range(4)]
     q, k, v, do = (t.cuda() for t in host)
-    if args.layout == "zigzag" and N > 1:
-        idx = ra.zigzag_indices(w["s"], rank, N)
-    else:
-        idx = torch.arange(c) + rank * c
+    idx = shard_indices(args.layout, w["s"], rank, N)
     pos = idx.to(torch.int32).expand(b, c).contiguous().cuda()
     out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
     lse = torch.empty((b, h, c), dtype=torch.float32, device="cuda")
     mod = RaScoreMod()
     mod.kinds = _lib.RA_MOD_CAUSAL
     mod.q_pos = mod.kv_pos = pos.data_ptr()
-    seg = slopes = None
+    seg = slopes = seg_global = None
     if w["mask"] == "documents":
         lens = torch.tensor(document_lengths(w["s"]))
         seg_global = torch.repeat_interleave(torch.arange(len(lens)), lens)
@@ -365,6 +496,25 @@ def main():
         dist.all_gather_object(gathered, exposed_all[0])
         exposed_all = gathered
     impl_used = {1: "simt", 2: "tcgen05"}.get(lib.ra_last_impl(), "?")
+    # bytes this rank pushed over NVLink in the last step and the device time of those copies
+    push = [ring.last_push(False), ring.last_push(True) if backward else (0.0, 0.0)] if N > 1 else []
+    push_bytes, push_ms = sum(x[0] for x in push), sum(x[1] for x in push)
+    rotation = {"bytes_per_step": push_bytes, "push_ms": push_ms,
+                "gb_per_s_per_direction": (push_bytes / (push_ms * 1e-3) / 1e9) if push_ms > 0 else None}
+    # no bounded wait ran out (inside a kernel, or for a peer), and the results are right: sampled rows
+    # of this rank's out / L / dq / dk / dv against the CPU oracle, outside every timed region
+    status_bits = _lib.device_status()
+    verdict = parity_check(w, args, rank, N, {"out": out, "lse": lse, "dq": dq, "dk": dk, "dv": dv},
+                           None if seg_global is None else seg_global.numpy(),
+                           None if slopes is None else slopes.cpu().numpy(), backward)
+    verdict["device_status"] = status_bits
+    verdict["ring_aborted"] = bool(ring.aborted)
+    verdict["ok"] = verdict["ok"] and status_bits == 0 and not verdict["ring_aborted"]
+    per_rank = [{"parity": verdict, "rotation": rotation}]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, per_rank[0])
+        per_rank = gathered
 
     # end to end through the public API, host buffers in and out
     e2e = None
@@ -428,10 +578,44 @@ def main():
         t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # the last step's results on the host are the ones the device-resident path produced
+        # (dQ is summed by floating-point reductions in no fixed order: equal up to bf16 rounding)
+        same = all(torch.allclose(hst.float(), dev_t.cpu().float(), atol=2e-2, rtol=1e-2, equal_nan=True)
+                   for hst, dev_t in zip(host_out, (out, dq, dk, dv)))
+
+        # The same step with nothing overlapped: copy in, compute, copy out, one after the other on
+        # one stream (the latency of a single call with host buffers, not a throughput).
+        def inline_run(steps):
+            for _ in range(steps):
+                for dst, src in zip(dev_in[0], host_in):
+                    dst.copy_(src, non_blocking=True)
+                dev = [x.detach().requires_grad_(backward) for x in dev_in[0][:3]]
+                o = ra.ring_attention(dev[0], dev[1], dev[2], ring, bias_fn=sm, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
+                                      block_impl=args.block_impl, plan=plan)
+                if backward:
+                    o.backward(dev_in[0][3])
+                results = (o.detach(), dev[0].grad, dev[1].grad, dev[2].grad) if backward else (o.detach(),)
+                for dst, src in zip(host_out, results):
+                    dst.copy_(src, non_blocking=True)
+
+        inline_run(1)
+        barrier()
+        i0, i1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        i0.record()
+        inline_run(min(args.steps, 3))
+        i1.record()
+        barrier()
+        ti = torch.tensor([i0.elapsed_time(i1) / min(args.steps, 3)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ti, op=dist.ReduceOp.MAX)
+        h2d = sum(x.numel() * x.element_size() for x in host_in)
+        d2h = sum(x.numel() * x.element_size() for x in host_out)
         e2e = {"value": b * w["s"] / (float(t.item()) * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
-               "d2h_bytes_per_step": sum(x.numel() * x.element_size() for x in host_out), "ms_per_step": float(t.item()),
-               "copies": "own streams, double-buffered on the device, inside the timed region"}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": float(t.item()),
+               "copies": "own streams, double-buffered on the device, inside the timed region",
+               "inline_ms_per_step": float(ti.item()),
+               "host_gb_per_s_each_way_all_ranks": world * h2d / (float(t.item()) * 1e-3) / 1e9,
+               "matches_device_resident_results": bool(same), "host": host_info}
 
     if rank == 0:
         pk = peaks()
@@ -447,8 +631,17 @@ def main():
         # dominant kernel: the backward block where the workload has a backward pass
         dom_ms, dom_flops, dom_name = (bwd_ms, bwd_flops_launch, "backward") if backward else (fwd_ms, fwd_flops_launch, "forward")
         achieved = dom_flops / (dom_ms * 1e-3) / 1e12
-        peak = pk["sustained"] if dom_ms > 5 else pk["burst"]
-        headline = args.workload in ("causal_32k", "causal_8k") and impl_used == "tcgen05"
+        # the step is seconds of back-to-back launches at the power cap: the sustained figure is the
+        # denominator at every N; the fraction of the burst figure is printed beside it
+        peak = pk["sustained"]
+        # DRAM bytes and FLOPs of the ncu capture of the dominant kernel (small causal case), kept next to
+        # its summary; traffic of one launch here = capture bytes scaled by the visible-pair count
+        capture = None
+        cap_path = os.path.join(ROOT, "profiles", "tc_bwd_kernel_causal_8k.json")
+        if args.workload in ("causal_32k", "causal_8k") and impl_used == "tcgen05" and os.path.exists(cap_path):
+            capture = json.load(open(cap_path))
+        parity_all = [x["parity"] for x in per_rank]
+        rates = [x["rotation"]["gb_per_s_per_direction"] for x in per_rank if x["rotation"]["gb_per_s_per_direction"]]
         line = {
             "metric": metric_name(w), "value": b * w["s"] / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": N,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
@@ -459,10 +652,9 @@ def main():
             "roofline": {
                 "bound": "tensor", "kernel": f"{impl_used} {dom_name} block", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of this kernel from the ncu capture of the 8k-token
-                # case (profiles/tc_bwd_kernel_causal_8k.md: 3.00 GB), scaled by the visible-pair count of a launch
-                "traffic": (3.00e9 * bwd_flops_launch / 1.3746e12) if headline else None,
-                "peak_source": f"{pk['source']} bf16 cuBLAS, {'sustained' if dom_ms > 5 else 'burst'}",
+                "frac_sustained": achieved / pk["sustained"], "frac_burst": achieved / pk["burst"],
+                "traffic": (capture["dram_bytes"] * bwd_flops_launch / capture["flops"]) if capture else None,
+                "peak_source": f"{pk['source']} bf16 cuBLAS, sustained ({pk['sustained']}; burst {pk['burst']})",
                 "launch_ms": dom_ms, "flops_per_launch": dom_flops,
                 "launches_per_step": int(bwd_blocks[1] if backward else fwd_blocks[1]),
                 "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
@@ -470,6 +662,18 @@ def main():
             "exposed_comm_ms": max(exposed_all), "exposed_comm_frac": max(exposed_all) / step_ms,
             "exposed_comm_ms_per_rank": exposed_all,
             "gpu_launches": int(launches),
+            "parity": {"ok": all(x["ok"] for x in parity_all), "max_excess": max(x["max_excess"] for x in parity_all),
+                       "rows": sum(x["rows"] for x in parity_all), "key_rows": sum(x["key_rows"] for x in parity_all),
+                       "bound": "2e-2 abs + 1e-2 rel against the float64 oracle on the bf16 inputs"
+                                if w["dtype"] == "bf16" else "bf16 bound applied to fp32 results",
+                       "device_status": [x["device_status"] for x in parity_all], "per_rank": parity_all},
+            "rotation": {"transport": ring.transport, "bytes_per_step_per_rank": per_rank[0]["rotation"]["bytes_per_step"],
+                         "gb_per_s_per_direction_min": min(rates) if rates else None,
+                         "gb_per_s_per_direction_mean": (sum(rates) / len(rates)) if rates else None,
+                         "link_peak_gb_per_s": 770.0,
+                         "note": "bytes this rank pushed to peers / device time of those peer copies on the transfer "
+                                 "stream (events around each copy), last timed step; 770 GB/s is the measured peer-copy "
+                                 "rate per direction on this pool"},
             "ring_plan": plan.matrix() if plan is not None else None,
             "clocks": clocks.summary(),
         }
@@ -478,9 +682,12 @@ def main():
         if N == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)
+    failed = not all(x["parity"]["ok"] for x in per_rank)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("parity check failed: see the `parity` object of the JSON line")
 
 
 if __name__ == "__main__":

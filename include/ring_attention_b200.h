@@ -42,6 +42,18 @@ extern "C" {
 #define RA_MOD_ALIBI 8u    /* add -slope[h] * (q_pos - kv_pos)  (a bias_fn, ring.py:107) */
 #define RA_MOD_WINDOW 16u  /* keep q_pos - kv_pos < window      (a bias_fn, ring.py:107) */
 #define RA_MOD_DENSE 32u   /* add a materialised bias tile      (ring.py:60-61) */
+/* Gradients of a (batch, head) that has a query row which sees no key at all.  The reference
+ * forms p = exp(s + bias - L) with s + bias = -inf and L = -inf for every pair of such a row
+ * (ring.py:146): NaN, which reaches dQ of that row and, through the sums over queries, dK and dV
+ * of EVERY key of that (batch, head), in every block of the ring.  The compiled-in masks define
+ * p = 0 on a masked pair instead, so such rows contribute nothing (the useful behaviour:
+ * padding rows do not destroy a batch).  With this bit set the backward calls reproduce the
+ * reference: after each block, dQ of the rows whose L is -inf and dK, dV of the whole
+ * (batch, head) are set to NaN.  It costs one more small kernel per block, switches off the
+ * ring-of-one shortcut that writes dK/dV straight in the result type, and makes the ring calls
+ * ignore a plan (the reference runs every step).  The dense-tile path (RA_MOD_DENSE) has the
+ * reference behaviour with or without it. */
+#define RA_MOD_STRICT_NAN 64u
 
 /* kernel families; RA_IMPL_AUTO picks tcgen05 whenever the shape allows it */
 #define RA_IMPL_AUTO 0
@@ -127,8 +139,11 @@ int ra_fwd_block(const ra_shape_t* shape, const ra_tensor_t* q, const ra_tensor_
  *   - It serves only calls the tcgen05 forward takes (bf16, head dim 64 or 128, lq and lk
  *     multiples of 128, no dense bias); anything else is refused with a negative code.
  *   - Limit: shape->b * (lq/128 + lk/128) <= RA_STATIC_MAX_TILES, else -41 and nothing runs.
- *   - The first call on each device looks up the array's device address (with that device
- *     current); make that first call outside any stream capture.
+ *     Calls without a mask or ALiBi (mod NULL or kinds 0) read no summaries, never touch the
+ *     array and have no such limit.
+ *   - The first call on each device looks up the device addresses of the array and of the
+ *     library's status word (with that device current); make that first call outside any
+ *     stream capture.
  *   - All calls share the array, which keeps the previous call's contents.  Each call
  *     rewrites every entry it later reads, so nothing needs clearing, but calls that
  *     overlap on the GPU (two streams, two threads) race on it: serialise them.
@@ -178,6 +193,40 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
 int ra_ring_destroy(ra_ring_t* ring);
 int ra_ring_rank(const ra_ring_t* ring);
 int ra_ring_size(const ra_ring_t* ring);
+
+/* Which transport the ring ended up with: 0 = ring of one (none), 1 = peer copies over CUDA
+ * IPC mappings, 2 = NCCL send/recv.  Peer copies are the default; the ring falls back to NCCL
+ * as a whole (every rank agrees) when RA_TRANSPORT=nccl is set or when some rank cannot export
+ * or map a peer's buffers (no peer access between two of the GPUs, GPUs of different nodes). */
+int ra_ring_transport(const ra_ring_t* ring);
+
+/* Allocates, ahead of time, everything ra_ring_fwd (and, with backward != 0, ra_ring_bwd)
+ * keeps in the handle for calls of this shape: the fp32 carried state (ring.py:124-126), the
+ * gradient accumulators (ring.py:198-200), the double buffers that receive the other ranks'
+ * K/V blocks (the operands of ring.py:120) and dK/dV contributions, and, with the peer-copy
+ * transport, the exchange and mapping of their IPC handles.  This is the only place where the
+ * ring calls cudaMalloc and synchronises the device: after it, ring calls of the same or a
+ * smaller shape allocate nothing and never synchronise (a host that runs inside a framework's
+ * custom call can reserve at set-up).  Without it the first call at each larger shape does the
+ * same work itself.  Collective when nranks > 1: every rank calls it with the same shape.
+ * Only which kv-side arrays of mod are non-NULL matters (they travel with K/V); mod may be NULL. */
+int ra_ring_reserve(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod_t* mod, int32_t backward);
+
+/* Bound of one wait for a peer (a K/V block or a dK/dV contribution that has not arrived, a
+ * buffer a peer has not released), in milliseconds of SM clock at 2 GHz.  Default: the
+ * environment variable RA_RING_WAIT_MS when the ring is created, else 10000.  A wait that runs
+ * out sets bit 16 of the device status word (ra_device_status) and the ring's abort word: from
+ * then on the ring's kernels neither wait nor announce anything to the peers, whose own waits
+ * run out in turn.  What the call computed after the wait is undefined (a block that never
+ * arrived was read, or a buffer a late peer still read was overwritten), and the flag counters
+ * of the ranks are out of step: destroy the ring on every rank and create a new one. */
+int ra_ring_set_wait_ms(ra_ring_t* ring, int32_t ms);
+/* 1 when a wait of this ring has run out (synchronous small copy from the device), else 0. */
+int ra_ring_aborted(ra_ring_t* ring);
+/* Diagnostic: enqueues the ring's bounded wait on a counter that nothing ever advances, so that
+ * the time-out path can be exercised without a peer (set a short bound first).  The ring is
+ * aborted afterwards, exactly as after a real time-out. */
+int ra_ring_probe_wait(ra_ring_t* ring, void* stream);
 
 /* Host-only schedule: which rank's K/V block this rank works on at step t
  * ((rank - t) mod nranks: ring.py:54 with the scan of ring.py:128-132). */
@@ -240,6 +289,12 @@ int ra_ring_last_timing(ra_ring_t* ring, int32_t backward, float* total_ms, floa
  * its steps, and how many there were.  Timing must be on; the two directions are kept
  * apart so that a forward + backward step can be queried once, after it ended. */
 int ra_ring_last_block_ms(ra_ring_t* ring, int32_t backward, float* block_ms, int32_t* launches);
+/* Peer-copy transport: bytes this rank pushed to other ranks (K/V blocks, and dK/dV
+ * contributions in the backward: the traffic of ring.py:120 and :195) during the last forward /
+ * backward ring call, and the device time of those copies on the transfer stream, event to
+ * event.  bytes / push_ms is the NVLink rate per direction the rotation achieved.  Timing
+ * must be on. */
+int ra_ring_last_push(ra_ring_t* ring, int32_t backward, double* bytes, float* push_ms);
 
 #ifdef __cplusplus
 }

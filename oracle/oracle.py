@@ -410,3 +410,120 @@ def timed_cpu_ring_causal(b, h, s, d, nranks, seed=0, dtype=np.float32):
     outs, lses = ring_attention_fwd(qs, ks, vs, fn, qk, kk, dtype=dtype, block_fn=fwd_block_mm)
     ring_attention_bwd(qs, ks, vs, outs, lses, dos, fn, qk, kk, dtype=dtype, block_fn=bwd_block_mm)
     return time.perf_counter() - t0
+
+
+# --------------------------------------------------------------------------------------
+# Sampled rows of a long sequence.  A dense float64 oracle over 32k - 1M tokens is out of
+# reach, but single rows are cheap: a query row attends to all keys in O(S d), and the
+# gradient of a key row needs L and delta only of the queries that see it.  Same math as
+# mha / mha_grads above (ring_test.py:26-42 and its jax.grad), one (batch, head) at a time,
+# tokens in position order (token i has position i), with the masks of score_mod_bias.
+# --------------------------------------------------------------------------------------
+def _visible(qi, kj, seg, window, causal):
+    """[len(qi), len(kj)] mask of visible pairs between query positions qi and key positions kj."""
+    rel = qi[:, None] - kj[None, :]
+    vis = np.ones(rel.shape, bool)
+    if causal:
+        vis &= rel >= 0
+    if seg is not None:
+        vis &= seg[qi][:, None] == seg[kj][None, :]
+    if window:
+        vis &= rel < window
+    return vis, rel
+
+
+def sampled_rows(q, k, v, do, scale, q_rows, k_rows, seg=None, window=0, slope=None, causal=True, blk=1024,
+                 score_dtype=np.float64):
+    """q, k, v, do: [S, d] float64 of one (batch, head), token i at position i.
+
+    Returns out, L, dq of the query rows `q_rows` and dk, dv of the key rows `k_rows`
+    (either list may be empty).  `slope`: ALiBi slope of this head (bias -slope * (i - j)).
+    `score_dtype` float32 makes the wide score products of the dk/dv part cheaper; the
+    per-row parts are always float64.
+    """
+    S = q.shape[0]
+    q_rows = np.asarray(q_rows, np.int64)
+    k_rows = np.asarray(k_rows, np.int64)
+    allk = np.arange(S)
+    res = {}
+
+    def scores(qi, lo, hi, dtype=np.float64):
+        kj = allk[lo:hi]
+        s = (q[qi].astype(dtype) @ k[lo:hi].astype(dtype).T).astype(np.float64) * scale
+        vis, rel = _visible(qi, kj, seg, window, causal)
+        if slope is not None:
+            s = s - slope * rel
+        return np.where(vis, s, NEG_INF), vis
+
+    seg_sorted = seg is not None and bool(np.all(np.diff(seg) >= 0))  # packed documents
+
+    def key_range(qi):
+        """A range of keys that holds every key some query of qi can see (only a cost bound)."""
+        lo, hi = 0, S
+        if causal:
+            hi = int(qi.max()) + 1
+        if window and causal:
+            lo = max(0, int(qi.min()) - window + 1)
+        if seg_sorted:
+            lo = max(lo, int(np.searchsorted(seg, seg[qi.min()], side="left")))
+            hi = min(hi, int(np.searchsorted(seg, seg[qi.max()], side="right")))
+        return lo, hi
+
+    if q_rows.size:
+        outs, Ls, dqs = [], [], []
+        for i in q_rows:
+            qi = np.array([i])
+            lo, hi = key_range(qi)
+            s, _ = scores(qi, lo, hi)
+            s = s[0]
+            with np.errstate(invalid="ignore", divide="ignore"):
+                m = s.max()
+                p = np.exp(s - m)
+                l = p.sum()
+                a = p / l
+                o = a @ v[lo:hi]
+                dp = v[lo:hi] @ do[i]
+                ds = a * (dp - do[i] @ o) * scale
+                outs.append(o)
+                Ls.append(m + np.log(l))
+                dqs.append(ds @ k[lo:hi])
+        res["out"], res["L"], res["dq"] = np.array(outs), np.array(Ls), np.array(dqs)
+
+    if k_rows.size:
+        # queries that see at least one sampled key
+        seen = np.zeros(S, bool)
+        for j in k_rows:
+            vis, _ = _visible(allk, np.array([j]), seg, window, causal)
+            seen |= vis[:, 0]
+        I = np.nonzero(seen)[0]
+        L = np.full(S, np.nan)
+        delta = np.full(S, np.nan)
+        for c0 in range(0, I.size, blk):
+            qi = I[c0:c0 + blk]
+            lo, hi = key_range(qi)
+            s, _ = scores(qi, lo, hi, score_dtype)
+            m = s.max(-1)
+            p = np.exp(s - m[:, None])
+            l = p.sum(-1)
+            L[qi] = m + np.log(l)
+            delta[qi] = np.einsum("id,id->i", (p / l[:, None]) @ v[lo:hi], do[qi])
+        dks, dvs = [], []
+        for j in k_rows:
+            vis, rel = _visible(I, np.array([j]), seg, window, causal)
+            vis, rel = vis[:, 0], rel[:, 0]
+            qi = I[vis]
+            s = (q[qi] @ k[j]) * scale
+            if slope is not None:
+                s = s - slope * rel[vis]
+            p = np.exp(s - L[qi])
+            dvs.append(p @ do[qi])
+            ds = p * (do[qi] @ v[j] - delta[qi]) * scale
+            dks.append(ds @ q[qi])
+        res["dk"], res["dv"] = np.array(dks), np.array(dvs)
+    return res
+
+
+def bf16_excess(got, want, atol=2e-2, rtol=1e-2):
+    """Largest amount by which |got - want| exceeds atol + rtol * |want| (<= 0 means inside the bound)."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float((np.abs(got - want) - (atol + rtol * np.abs(want))).max()) if want.size else float("-inf")

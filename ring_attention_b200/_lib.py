@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libring_attention_b200.so")
 
 RA_DTYPE_F32, RA_DTYPE_BF16 = 0, 1
 RA_MOD_CAUSAL, RA_MOD_SEGMENT, RA_MOD_PREFIX, RA_MOD_ALIBI, RA_MOD_WINDOW, RA_MOD_DENSE = 1, 2, 4, 8, 16, 32
+RA_MOD_STRICT_NAN = 64
 RA_IMPL_AUTO, RA_IMPL_SIMT, RA_IMPL_TCGEN05 = 0, 1, 2
 RA_UNIQUE_ID_BYTES = 128
 
@@ -75,9 +76,15 @@ _SIGNATURES = {
     "ra_ring_use_plan": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ra_ring_rotate": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_void_p), _P(C.c_void_p), _P(C.c_int64),
                                  C.c_void_p]),
+    "ra_ring_transport": (C.c_int, [C.c_void_p]),
+    "ra_ring_reserve": (C.c_int, [C.c_void_p, _P(RaShape), _P(RaScoreMod), C.c_int32]),
+    "ra_ring_set_wait_ms": (C.c_int, [C.c_void_p, C.c_int32]),
+    "ra_ring_aborted": (C.c_int, [C.c_void_p]),
+    "ra_ring_probe_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ra_ring_set_timing": (C.c_int, [C.c_void_p, C.c_int32]),
     "ra_ring_last_timing": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_float), _P(C.c_float)]),
     "ra_ring_last_block_ms": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_float), _P(C.c_int32)]),
+    "ra_ring_last_push": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_double), _P(C.c_float)]),
 }
 
 EXPORTS = tuple(_SIGNATURES)
@@ -102,6 +109,20 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
+
+
+RA_ERR_DEVICE_STATUS = 3
+
+
+def device_status() -> int:
+    """Synchronises the current device and returns (and clears) its kernel status word: 0 when no
+    bounded wait inside a kernel has run out since the last read (bits 0-10: the tcgen05 kernels'
+    own waits; bit 16: a ring's wait for a peer)."""
+    bits = C.c_uint32(0)
+    rc = lib.ra_device_status(C.byref(bits))
+    if rc not in (0, RA_ERR_DEVICE_STATUS):
+        check(rc)
+    return int(bits.value)
 
 
 def check(rc: int) -> None:

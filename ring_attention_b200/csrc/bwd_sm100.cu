@@ -14,11 +14,16 @@
 //   dV  += P^T dO         (TS MMA: A from TMEM, B = dO read MN-major) -> TMEM [256,256+D)
 //   dK  += dS^T Q         (SS MMA: B = Q read MN-major)               -> TMEM [256+D,256+2D)
 //   dQ^T = K^T dS^T       (SS MMA: A = K read MN-major, B = dS^T tile read MN-major; head dim 128)
-//                          -> TMEM [128,256), over dP^T; lane = head-dim index, so each warp adds
-//                             128 contiguous bytes of a dQ row to the fp32 accumulator per reduction.
+//                          -> TMEM [128,256), over dP^T; lane = head-dim index.  Each compute warp
+//                             copies its 32 head-dim lanes x 16 queries at a time into a small
+//                             shared-memory buffer and hands it to the TMA unit, which adds it to
+//                             the fp32 accumulator (tiled bulk reduce-add): the SM's load/store
+//                             path, which the MMAs' operand reads share, sees plain stores only.
 //                             (head dim 64 forms dQ = dS K instead and uses vector reductions.)
 // warps 0-7: compute (two warpgroups split the 128 query columns), warp 8: TMA producer,
 // warp 9: MMA issuer.
+// Grid: CTAs of a few (batch, head) pairs at a time, so that the Q / dO tiles and the dQ
+// accumulator rows that the resident CTAs stream stay in L2.
 #include <cstdio>
 #include <cstring>
 
@@ -33,38 +38,17 @@ using namespace ptx;
 
 constexpr int kBwdThreads = 320;
 
-// Optional timeline of one CTA (build with -DRA_TRACE): each TRACE(tag) appends
-// (tag, clock64) to a global buffer.  Used to find where a tile's time goes.
-#ifdef RA_TRACE
-}  // namespace
-__device__ unsigned long long g_trace[4][4096];
-__device__ unsigned int g_trace_n[4];
-namespace {
-#define TRACE(who, tag)                                                        \
-  do {                                                                         \
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                          \
-      unsigned int k_ = g_trace_n[who]++;                                      \
-      if (k_ < 2048) {                                                         \
-        g_trace[who][2 * k_] = (tag);                                          \
-        g_trace[who][2 * k_ + 1] = clock64();                                  \
-      }                                                                        \
-    }                                                                          \
-  } while (0)
-#else
-#define TRACE(who, tag) do {} while (0)
-#endif
 constexpr float kLog2e = 1.4426950408889634f;
-#ifndef RA_POLL_NS
-#define RA_POLL_NS 100
-#endif
-constexpr unsigned kProducerPollNs = RA_POLL_NS;
+constexpr unsigned kProducerPollNs = 100;
 
 struct BwdTcParams {
   CUtensorMap map_q, map_k, map_v, map_do;
+  CUtensorMap map_dq;  // fp32 [b*h*lq, 128], box {32, 16}: head dim 128 only
   BwdParams p;
   const TileMeta* meta_q;
   const TileMeta* meta_kv;
   int n_q_tiles, n_kv_tiles;
+  int group_heads;  // (batch, head) pairs whose CTAs are interleaved in the grid
   unsigned int* status;
 };
 
@@ -91,13 +75,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = kTileRows * 128;
   constexpr int DS_BYTES = kTileRows * kTileRows * 2;
+  // Head dim 128 keeps one dO stage (a dO tile is free after dV of its query tile, three MMA
+  // groups before the next tile's dP^T needs the next one) and spends the 32 KB on the dQ
+  // staging buffers: 8 compute warps x 2 buffers x [16 queries][32 head-dim lanes] fp32.
+  constexpr int DO_ST = D == 128 ? 1 : 2;
+  constexpr int DQ_STAGE_BYTES = D == 128 ? 8 * 2 * 16 * 32 * 4 : 0;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE_BYTES;
   uint8_t* sQ = sV + TILE_BYTES;          // 2 stages
-  uint8_t* sdO = sQ + 2 * TILE_BYTES;     // 2 stages
-  uint8_t* sdS = sdO + 2 * TILE_BYTES;    // [128 key rows][128 query cols] bf16, 2 panels, 128B swizzle
-  float* sL = reinterpret_cast<float*>(sdS + DS_BYTES);  // [2][128]
+  uint8_t* sdO = sQ + 2 * TILE_BYTES;     // DO_ST stages
+  uint8_t* sdS = sdO + DO_ST * TILE_BYTES;  // [128 key rows][128 query cols] bf16, 2 panels, 128B swizzle
+  float* sdQ = reinterpret_cast<float*>(sdS + DS_BYTES);
+  float* sL = reinterpret_cast<float*>(sdS + DS_BYTES + DQ_STAGE_BYTES);  // [2][128]
   float* sDelta = sL + 2 * kTileRows;                     // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * kTileRows);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
@@ -106,8 +96,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   const BwdParams& p = P.p;
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int bh_count = p.b * p.h;
-  const int bh = blockIdx.x % bh_count;
-  const int kt = blockIdx.x / bh_count;  // K/V tile; tile 0 has the most visible queries under a causal mask
+  // groups of group_heads (batch, head) pairs; inside a group the pairs alternate and the K/V
+  // tiles ascend (tile 0 has the most visible queries under a causal mask)
+  const int per_group = P.group_heads * P.n_kv_tiles;
+  const int grp = blockIdx.x / per_group, in_grp = blockIdx.x - grp * per_group;
+  const int grp_n = min(P.group_heads, bh_count - grp * P.group_heads);
+  const int bh = grp * P.group_heads + in_grp % grp_n;
+  const int kt = in_grp / grp_n;
   const int hh = bh % p.h, bb = bh / p.h;
   const uint32_t kinds = p.mod.kinds;
   const bool masked = (kinds & kMetaKinds) != 0;  // the tile summaries are read
@@ -171,6 +166,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       prefetch_tensormap(&P.map_k);
       prefetch_tensormap(&P.map_v);
       prefetch_tensormap(&P.map_do);
+      if constexpr (D == 128) prefetch_tensormap(&P.map_dq);
     }
     const int i = next_active(0) & kTileIdx;
     if (i < P.n_q_tiles && lane == 0) {
@@ -191,7 +187,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       uint32_t ready = 0;
       if (lane == 0) {
         if (qi < P.n_q_tiles && mbar_test(&bars[Q_EMPTY0 + (qn & 1)], ((qn >> 1) & 1) ^ 1)) ready |= 1u;
-        if (doi < P.n_q_tiles && mbar_test(&bars[DO_EMPTY0 + (don & 1)], ((don >> 1) & 1) ^ 1)) ready |= 2u;
+        if (doi < P.n_q_tiles && mbar_test(&bars[DO_EMPTY0 + don % DO_ST], ((don / DO_ST) & 1) ^ 1)) ready |= 2u;
       }
       ready = __shfl_sync(0xffffffffu, ready, 0);
       if (ready & 1u) {
@@ -208,7 +204,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       }
       if (ready & 2u) {
         if (lane == 0) {
-          const int s = don & 1;
+          const int s = don % DO_ST;
           mbar_arrive_expect_tx(&bars[DO_FULL0 + s], TILE_BYTES);
           for (int pn = 0; pn < PANELS; ++pn)
             tma_load_4d(sdO + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_do, &bars[DO_FULL0 + s], pn * 64, hh, doi * kTileRows, bb);
@@ -283,15 +279,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       // so that the compute warps form P(n+1) under dQ(n)/dK(n), drain dQ(n) under dK(n), and
       // form dS(n+1) under dV(n+1)/S(n+2).
       bool ok = true;
-#ifdef RA_PROF
-      long long pw[5] = {0, 0, 0, 0, 0}, pt0 = clock64(), pa;
-      int ptiles = 0;
-#define PROF_BEGIN() pa = clock64()
-#define PROF_END(slot) pw[slot] += clock64() - pa
-#else
-#define PROF_BEGIN() do {} while (0)
-#define PROF_END(slot) do {} while (0)
-#endif
       int i = next_active(0) & kTileIdx;
       if (i < P.n_q_tiles) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
@@ -310,25 +297,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         }
         for (int n = 0; ok; ++n) {
           const int s = n & 1, sn = (n + 1) & 1;
+          const int dsn = (n + 1) % DO_ST;  // dO stage and phase of tile n + 1
+          const uint32_t dphn = ((n + 1) / DO_ST) & 1;
           const uint32_t par = n & 1;
           const int inext = next_active(i + 1) & kTileIdx;
           const bool has_next = inext < P.n_q_tiles;
-          TRACE(0, 1);
           if (has_next) {
-            PROF_BEGIN();
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
-            PROF_END(0);
             tc_fence_after();
-            TRACE(0, 2);
             issue_s(sn);
           }
-          TRACE(0, 3);
           // dQ = dS K (into the dP^T columns), dK += dS^T Q
-          PROF_BEGIN();
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_READY], par, abort_flag, P.status, kStBwdMma)))) break;
-          PROF_END(1);
           tc_fence_after();
-          TRACE(0, 4);
           if constexpr (D == 128) {
             // dQ^T = K^T dS^T: lane = head-dim index, column = query, so that a warp's reduction
             // instruction covers 128 contiguous bytes of one dQ row
@@ -341,11 +322,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
               mma_ss_warp(tmem_dP, desc_from_lo(ds_mn + mn_off(kk)), desc_from_lo(k_mn + mn_off(kk)), idesc_dq, kk > 0);
           }
           tc_commit_warp(&bars[DQ_FULL]);
-#ifdef RA_TRACE_SERIAL
-          TRACE(0, 20);
-          mbar_wait(&bars[DQ_FULL], par, abort_flag, P.status, kStBwdMma);
-          TRACE(0, 21);
-#endif
           {
             const uint32_t b0 = q_mn + s * kStage16;
 #pragma unroll
@@ -355,43 +331,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           }
           tc_commit_warp(&bars[Q_EMPTY0 + s]);
           tc_commit_warp(&bars[DS_FREE]);
-#ifdef RA_TRACE_SERIAL
-          TRACE(0, 22);
-          mbar_wait(&bars[DS_FREE], par, abort_flag, P.status, kStBwdMma);
-          TRACE(0, 23);
-#endif
-          TRACE(0, 5);
           if (!has_next) break;
-          PROF_BEGIN();
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma)))) break;
-          PROF_END(2);
-          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DO_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DO_FULL0 + dsn], dphn, abort_flag, P.status, kStBwdMma)))) break;
           tc_fence_after();
-          TRACE(0, 6);
-          issue_dp(sn);
-          TRACE(0, 7);
-          PROF_BEGIN();
+          issue_dp(dsn);
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[P_READY], par ^ 1, abort_flag, P.status, kStBwdMma)))) break;
-          PROF_END(3);
-#ifdef RA_PROF
-          ++ptiles;
-#endif
           tc_fence_after();
-          TRACE(0, 8);
-          issue_dv(sn, false);
-          tc_commit_warp(&bars[DO_EMPTY0 + sn]);
+          issue_dv(dsn, false);
+          tc_commit_warp(&bars[DO_EMPTY0 + dsn]);
           i = inext;
         }
         if (ok) tc_commit_warp(&bars[DKDV_FULL]);
       }
-#ifdef RA_PROF
-      if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == 300) && ptiles > 0) {
-        const long long tot = clock64() - pt0;
-        printf("bwd CTA %d: %d tiles, %lld clk/tile; MMA warp waits per tile: Q_FULL %lld, DS_READY %lld, DQ_DRAINED %lld, P_READY %lld; issuing+other %lld\n",
-               blockIdx.x, ptiles, tot / ptiles, pw[0] / ptiles, pw[1] / ptiles, pw[2] / ptiles, pw[3] / ptiles,
-               (tot - pw[0] - pw[1] - pw[2] - pw[3]) / ptiles);
-      }
-#endif
     }
   } else {
     // ------------------------------------------------------------ compute (warps 0-7)
@@ -431,10 +383,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         // ---- dS^T = P^T * (dP^T - delta) of tile k-1 -> shared memory, 128-byte swizzle
         const int n = k - 1, s = n & 1;
         const float4* Dls = reinterpret_cast<const float4*>(sDelta + s * kTileRows + g * 64);
-        if (threadIdx.x == 0) TRACE(1, 10);
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
-        if (threadIdx.x == 0) TRACE(1, 11);
         tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
         tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
         tc_wait_ld();
@@ -457,7 +407,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(&bars[DS_READY]);
-        if (threadIdx.x == 0) TRACE(1, 12);
       }
       if (have_cur) {
         // ---- P^T = exp2(S^T * scale2 - L * log2e) of tile k on this warpgroup's 64 query columns
@@ -470,7 +419,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         const float4* Ls = reinterpret_cast<const float4*>(sL + s * kTileRows + g * 64);
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[S_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
-        if (threadIdx.x == 0) TRACE(1, 13);
         if (need_mask || (alibi && !alibi_inline)) {  // tiles that mix visible and masked pairs, ALiBi over scattered positions
           const int64_t q0 = (int64_t)bb * p.lq + (int64_t)i * kTileRows + g * 64;
           fixup_scores_tmem<false>(tmem_S + lane_off + g * 64, 64, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
@@ -511,27 +459,40 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars[P_READY]);
-        if (threadIdx.x == 0) TRACE(1, 14);
       }
       if (have_prev) {
         // ---- dQ of tile k-1: rows are queries; add this warpgroup's half of the columns
         const int n = k - 1;
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
-        if (threadIdx.x == 0) TRACE(1, 15);
         if constexpr (D == 128) {
           // dQ^T: this thread owns head-dim index r; columns are the tile's queries, this warpgroup's 64
-          float* dq_col = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + g * 64) * D + r;
           tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
           tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
           tc_wait_ld();
-          // the values are in registers: hand the TMEM columns back before the reductions, so that
-          // dP^T of the next tile does not wait for them
+          // the values are in registers: hand the TMEM columns back first, so that dP^T of the
+          // next tile does not wait for what follows
           tc_fence_before();
           mbar_arrive(&bars[DQ_DRAINED]);
+          // 4 rounds of 16 queries through this warp's two staging buffers; the TMA unit adds
+          // each [16 queries][32 lanes] box to the accumulator rows
+          float* stage = sdQ + warp * (2 * 16 * 32);
+          const int dq_row0 = (int)(qrow_base + (int64_t)i_prev * kTileRows + g * 64);
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            atomicAdd(dq_col + (int64_t)c * D, __uint_as_float(sv[c >> 5][c & 31]) * p.scale);  // no return value: a RED
+          for (int j = 0; j < 4; ++j) {
+            float* buf = stage + (j & 1) * (16 * 32);
+            if (lane == 0) bulk_wait_group_read<1>();  // the reduce issued two rounds ago has read this buffer
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              buf[c * 32 + lane] = __uint_as_float(sv[(j * 16 + c) >> 5][(j * 16 + c) & 31]) * p.scale;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_2d(&P.map_dq, buf, (warp & 3) * 32, dq_row0 + j * 16);
+              bulk_commit_group();
+            }
+          }
         } else {
           constexpr int HALF = D / 2;
           float* dq_row = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + r) * D + g * HALF;
@@ -544,7 +505,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           tc_fence_before();
           mbar_arrive(&bars[DQ_DRAINED]);
         }
-        if (threadIdx.x == 0) TRACE(1, 16);
       }
       if (!have_cur) break;
       i_prev = i_cur;
@@ -562,6 +522,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       float* dk_row = p.dk + krow * D + g * HALF;
       float* dv_row = p.dv + krow * D + g * HALF;
       const bool direct = p.dk_out.ptr != nullptr;  // ring of one: results go out in the input dtype
+      const bool fresh = p.overwrite != 0;          // the fp32 buffers hold nothing yet: store, do not add
       __nv_bfloat16* dk_o = direct ? (__nv_bfloat16*)p.dk_out.ptr + (int64_t)bb * p.dk_out.sb +
                                          (int64_t)kv_row * p.dk_out.sl + (int64_t)hh * p.dk_out.sh + g * HALF
                                    : nullptr;
@@ -583,7 +544,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         } else {
 #pragma unroll
           for (int e = 0; e < 8; e += 4) {
-            float4 cur = *reinterpret_cast<float4*>(dk_row + c * 8 + e);
+            float4 cur = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<float4*>(dk_row + c * 8 + e);
             cur.x += __uint_as_float(a[e]) * p.scale;
             cur.y += __uint_as_float(a[e + 1]) * p.scale;
             cur.z += __uint_as_float(a[e + 2]) * p.scale;
@@ -603,7 +564,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         } else {
 #pragma unroll
           for (int e = 0; e < 8; e += 4) {
-            float4 cur = *reinterpret_cast<float4*>(dv_row + c * 8 + e);
+            float4 cur = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<float4*>(dv_row + c * 8 + e);
             cur.x += __uint_as_float(a[e]);
             cur.y += __uint_as_float(a[e + 1]);
             cur.z += __uint_as_float(a[e + 2]);
@@ -625,6 +586,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         *reinterpret_cast<uint4*>(dv_o + c * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
+    else if (ok && n == 0 && p.overwrite) {
+      // no query tile sees this K/V tile and the fp32 buffers were not cleared: its rows are zero
+      constexpr int HALF = D / 2;
+      const int64_t krow = ((int64_t)bb * p.h + hh) * p.lk + kv_row;
+      float4* dk_row = reinterpret_cast<float4*>(p.dk + krow * D + g * HALF);
+      float4* dv_row = reinterpret_cast<float4*>(p.dv + krow * D + g * HALF);
+#pragma unroll 1
+      for (int c = 0; c < HALF / 4; ++c) dk_row[c] = dv_row[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // the staging buffers must outlive the reduce-adds that read them
+    if constexpr (D == 128) {
+      if (lane == 0) bulk_wait_group<0>();
+    }
   }
 
   tc_fence_before();
@@ -638,7 +612,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 
 template <int D>
 cudaError_t launch_bwd(const BwdTcParams& P, cudaStream_t s) {
-  constexpr size_t kSmem = 6 * kTileRows * D * 2 + kTileRows * kTileRows * 2 + 4 * kTileRows * 4 + NUM_BARS * 8 + 64;
+  constexpr size_t kSmem = (D == 128 ? 5 : 6) * kTileRows * D * 2 + kTileRows * kTileRows * 2 +
+                           (D == 128 ? 8 * 2 * 16 * 32 * 4 : 0) + 4 * kTileRows * 4 + NUM_BARS * 8 + 64;
   constexpr size_t kRequest = kSmem < 120 * 1024 ? 120 * 1024 : kSmem;  // one CTA per SM: it owns all of TMEM
   auto kern = tc_bwd_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRequest);
@@ -667,6 +642,7 @@ const char* tc_bwd_unsupported_reason(const BwdParams& p, int dtype) {
       (reinterpret_cast<uintptr_t>(p.dv) & 15))
     return "lse/delta/dq/dk/dv need 16-byte aligned bases";
   if (!(p.scale > 0.f)) return "sm_scale must be positive";
+  if ((int64_t)p.b * p.h * p.lq >= (int64_t)1 << 31) return "b * h * lq must stay below 2^31";
   if (p.dk_out.ptr && (!aligned16(p.dk_out) || !p.dv_out.ptr || !aligned16(p.dv_out)))
     return "dk/dv results need 16-byte aligned bases and strides";
   return nullptr;
@@ -684,32 +660,34 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
       !make_tile_map(&P.map_v, p.v, p.b, p.lk, p.h, p.dv_dim, kTileRows, &why) ||
       !make_tile_map(&P.map_do, p.dout, p.b, p.lq, p.h, p.dv_dim, kTileRows, &why))
     return cudaErrorNotSupported;
+  if (p.dk_dim == 128 &&
+      !make_f32_rows_map(&P.map_dq, p.dq, (int64_t)p.b * p.h * p.lq, 128, 32, 16, &why))
+    return cudaErrorNotSupported;
   P.status = device_status_word();
   if (!P.status) return cudaErrorInvalidSymbol;
+  // CTAs that are resident together should stream the same Q / dO tiles and add into the same
+  // dQ rows: interleave only as many (batch, head) pairs as keep those within about 64 MB of L2
+  const int64_t per_head = (int64_t)p.lq * p.dk_dim * (2 + 2 + 4);
+  int64_t group = (64ll << 20) / (per_head > 0 ? per_head : 1);
+  if (group < 1) group = 1;
+  if (group > (int64_t)p.b * p.h) group = (int64_t)p.b * p.h;
+  P.group_heads = (int)group;
   TileMeta* meta = nullptr;
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
   if (p.mod.kinds & kMetaKinds) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
     if ((e = scratch_alloc((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
     TileMeta* mq = meta;
     TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
-    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess) return e;
-    if ((e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s)) != cudaSuccess) return e;
+    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) == cudaSuccess)
+      e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s);
     P.meta_q = mq;
     P.meta_kv = mk;
   }
-  e = p.dk_dim == 128 ? launch_bwd<128>(P, s) : launch_bwd<64>(P, s);
-  if (meta) cudaFreeAsync(meta, s);
+  if (e == cudaSuccess) e = p.dk_dim == 128 ? launch_bwd<128>(P, s) : launch_bwd<64>(P, s);
+  if (meta) cudaFreeAsync(meta, s);  // stream-ordered: after the kernels above, also when one failed to launch
   return e;
 }
 
 }  // namespace ra
 
-#ifdef RA_TRACE
-extern "C" int ra_debug_trace(unsigned long long* buf, unsigned int* counts) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(buf, ra::g_trace, sizeof(unsigned long long) * 4 * 4096);
-  cudaMemcpyFromSymbol(counts, ra::g_trace_n, sizeof(unsigned int) * 4);
-  return 0;
-}
-#endif

@@ -57,6 +57,10 @@ struct BwdParams {
   // whole backward for these keys (ring of one) and the kernel stores dK, dV in the input
   // dtype straight to the result tensors; dk / dv above are then not touched.
   TensorView dk_out, dv_out;
+  // Optional: dk / dv above hold nothing yet and this call defines them (stores instead of
+  // read-add-write, zeros for key rows that no query sees), so the caller need not clear them.
+  // The tcgen05 kernel does it in its epilogue; for the CUDA-core kernel the dispatcher clears first.
+  int32_t overwrite;
 };
 
 // Launchers implemented in the .cu files.  Each returns a cudaError_t.
@@ -69,6 +73,10 @@ cudaError_t launch_delta(int b, int h, int lq, int dv, TensorView out, TensorVie
 cudaError_t launch_cast_from_f32(int b, int h, int len, int d, const float* src, TensorView dst,
                                  int dtype, cudaStream_t s);
 cudaError_t launch_add_f32(float* dst, const float* src, int64_t n, cudaStream_t s);
+// One block per (batch, head): where some query row has L = -inf, dq of those rows and all of
+// dk, dv of that (batch, head) become NaN (what ring.py:146 produces for such rows).
+cudaError_t launch_strict_nan(int b, int h, int lq, int lk, int dk_dim, int dv_dim, const float* lse, float* dq,
+                              float* dk, float* dv, cudaStream_t s);
 
 void count_launch(int n = 1);
 

@@ -499,8 +499,17 @@ cudaError_t scratch_alloc(void** ptr, size_t bytes, cudaStream_t s) {
 }
 
 unsigned int* device_status_word() {
-  unsigned int* ptr = nullptr;
-  if (cudaGetSymbolAddress((void**)&ptr, g_status_word) != cudaSuccess) return nullptr;
+  // looked up once per device, with that device current (the symbol's name is a host-side
+  // handle, not an address a kernel can use)
+  constexpr int kMaxDevices = 64;
+  static unsigned int* cache[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  unsigned int* ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    if (cudaGetSymbolAddress((void**)&ptr, g_status_word) != cudaSuccess || !ptr) return nullptr;
+    __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
+  }
   return ptr;
 }
 
@@ -522,6 +531,27 @@ bool make_tile_map(CUtensorMap* map, const TensorView& t, int b, int len, int h,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     *why = "the driver refused the tensor map for these strides";
+    return false;
+  }
+  return true;
+}
+
+bool make_f32_rows_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int box_cols, int box_rows,
+                       const char** why) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    *why = "cuTensorMapEncodeTiled is not available from this driver";
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *why = "the driver refused the tensor map of the fp32 accumulator";
     return false;
   }
   return true;
@@ -566,19 +596,19 @@ cudaError_t tc_fwd_block(const FwdParams& p, cudaStream_t s) {
   P.status = device_status_word();
   if (!P.status) return cudaErrorInvalidSymbol;
   TileMeta* meta = nullptr;
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
   if (p.mod.kinds & kMetaKinds) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
     if ((e = scratch_alloc((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
     TileMeta* mq = meta;
     TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
-    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) != cudaSuccess) return e;
-    if ((e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s)) != cudaSuccess) return e;
+    if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) == cudaSuccess)
+      e = launch_tile_meta(mk, p.mod.kv_pos, p.mod.kv_seg, p.mod.kv_pre, p.b, p.lk, s);
     P.meta_q = mq;
     P.meta_kv = mk;
   }
-  e = p.dk == 128 ? launch_fwd<128>(P, s) : launch_fwd<64>(P, s);
-  if (meta) cudaFreeAsync(meta, s);
+  if (e == cudaSuccess) e = p.dk == 128 ? launch_fwd<128>(P, s) : launch_fwd<64>(P, s);
+  if (meta) cudaFreeAsync(meta, s);  // stream-ordered: after the kernels above, also when one failed to launch
   return e;
 }
 
@@ -666,8 +696,10 @@ extern "C" int ra_fwd_block_static(const ra_shape_t* shape, const ra_tensor_t* q
     return fail(-40, "ra_fwd_block_static serves only what the tcgen05 forward takes: %s", why);
   P.n_q_tiles = p.lq / kTileRows;
   P.n_kv_tiles = p.lk / kTileRows;
+  // the fixed array holds the tile summaries, which only calls with a mask or ALiBi read
+  const bool uses_scratch = (p.mod.kinds & kMetaKinds) != 0;
   const long long tiles = (long long)p.b * (P.n_q_tiles + P.n_kv_tiles);
-  if (tiles > kStaticMaxTiles)
+  if (uses_scratch && tiles > kStaticMaxTiles)
     return fail(-41, "ra_fwd_block_static: b * (lq/128 + lk/128) = %lld tiles exceeds the fixed scratch of %d tiles",
                 tiles, kStaticMaxTiles);
   const char* why = nullptr;
@@ -679,7 +711,7 @@ extern "C" int ra_fwd_block_static(const ra_shape_t* shape, const ra_tensor_t* q
   if (!P.status) return fail(RA_ERR_CUDA, "status word symbol not found");
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
-  if (p.mod.kinds & kMetaKinds) {
+  if (uses_scratch) {
     TileMeta* meta = nullptr;
     if ((e = static_tile_meta(&meta)) != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
     TileMeta* mq = meta;

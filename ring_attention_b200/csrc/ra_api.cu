@@ -55,7 +55,7 @@ int check_mod(const ra_score_mod_t* m, ModParams* out) {
   memset(out, 0, sizeof(*out));
   if (!m) return 0;
   const uint32_t known = RA_MOD_CAUSAL | RA_MOD_SEGMENT | RA_MOD_PREFIX | RA_MOD_ALIBI |
-                         RA_MOD_WINDOW | RA_MOD_DENSE;
+                         RA_MOD_WINDOW | RA_MOD_DENSE | RA_MOD_STRICT_NAN;
   if (m->kinds & ~known) return fail(-7, "score_mod: unknown kind bits 0x%x", m->kinds & ~known);
   // The same combinations ring_self_attention refuses (ring.py:368-374).
   if ((m->kinds & RA_MOD_CAUSAL) && (m->kinds & RA_MOD_PREFIX))
@@ -109,24 +109,41 @@ int run_fwd_block(const FwdParams& p, int dtype, cudaStream_t s) {
   return 0;
 }
 
+// ring.py:146 on a row whose L is -inf: see RA_MOD_STRICT_NAN.  Runs after the block kernel, on
+// the fp32 accumulators the block added into.
+static int strict_nan(const BwdParams& p, cudaStream_t s) {
+  if (!(p.mod.kinds & RA_MOD_STRICT_NAN) || (p.mod.kinds & RA_MOD_DENSE)) return 0;
+  cudaError_t e = launch_strict_nan(p.b, p.h, p.lq, p.lk, p.dk_dim, p.dv_dim, p.lse, p.dq, p.dk, p.dv, s);
+  if (e != cudaSuccess) return fail_cuda(e, "strict NaN pass");
+  return 0;
+}
+
 int run_bwd_block(const BwdParams& p, int dtype, cudaStream_t s) {
   int impl = g_impl;
+  if ((p.mod.kinds & RA_MOD_STRICT_NAN) && p.dk_out.ptr)
+    return fail(-44, "RA_MOD_STRICT_NAN needs the fp32 accumulators, not direct results");
   if (impl != RA_IMPL_SIMT) {
     const char* why = tc_bwd_unsupported_reason(p, dtype);
     if (!why) {
       cudaError_t e = tc_bwd_block(p, s);
       if (e == cudaSuccess) {
         g_last_impl = RA_IMPL_TCGEN05;
-        return 0;
+        return strict_nan(p, s);
       }
       if (e != cudaErrorNotSupported || impl == RA_IMPL_TCGEN05) return fail_cuda(e, "tcgen05 backward block");
     }
     if (why && impl == RA_IMPL_TCGEN05) return fail(-20, "tcgen05 backward does not take this call: %s", why);
   }
+  if (p.overwrite) {  // the CUDA-core kernel adds: clear what the caller left uncleared
+    cudaError_t e = cudaMemsetAsync(p.dk, 0, (size_t)p.b * p.h * p.lk * p.dk_dim * sizeof(float), s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(p.dv, 0, (size_t)p.b * p.h * p.lk * p.dv_dim * sizeof(float), s);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync");
+    count_launch(2);
+  }
   cudaError_t e = simt_bwd_block(p, dtype, s);
   if (e != cudaSuccess) return fail_cuda(e, "simt backward block");
   g_last_impl = RA_IMPL_SIMT;
-  return 0;
+  return strict_nan(p, s);
 }
 
 }  // namespace ra

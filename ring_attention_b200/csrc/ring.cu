@@ -156,8 +156,11 @@ struct FlagList {
 };
 
 // One thread; waits until *flag >= target.  Bounded: gives up after max_cycles SM cycles,
-// records it in the status word and returns, so the stream always drains.
-__global__ void wait_flag_kernel(const uint64_t* flag, uint64_t target, unsigned int* status, long long max_cycles) {
+// records it in the status word, raises the ring's abort word and returns, so the stream
+// always drains.  Once the abort word is up every later wait of the ring returns at once.
+__global__ void wait_flag_kernel(const uint64_t* flag, uint64_t target, unsigned int* status, unsigned int* abort_word,
+                                 long long max_cycles) {
+  if (*(volatile unsigned int*)abort_word) return;
   const long long t0 = clock64();
   while (true) {
     uint64_t v;
@@ -166,16 +169,22 @@ __global__ void wait_flag_kernel(const uint64_t* flag, uint64_t target, unsigned
     __nanosleep(100);
     if (clock64() - t0 > max_cycles) {
       atomicOr(status, kStRingWait);
+      atomicExch(abort_word, 1u);
+      __threadfence();
       return;
     }
   }
 }
 
 // Thread i publishes `value` to list.ptr[i] (own or peer memory) after everything that
-// preceded this kernel on its stream.
-__global__ void set_flags_kernel(FlagList list, uint64_t value) {
+// preceded this kernel on its stream -- unless a wait of this ring has run out: what the
+// stream did after that wait may have used a block that never arrived or overwritten one
+// that was still being read, and must not be announced as ready.  The peers' own waits then
+// run out in turn, so the failure is reported on every rank instead of spreading as data.
+__global__ void set_flags_kernel(FlagList list, uint64_t value, const unsigned int* abort_word) {
   const int i = threadIdx.x;
   if (i >= list.n) return;
+  if (*(volatile const unsigned int*)abort_word) return;
   __threadfence_system();
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(list.ptr[i]), "l"(value) : "memory");
 }
@@ -196,6 +205,7 @@ struct ra_ring_plan {
 struct ra_ring {
   int rank = 0, nranks = 1, device = 0;
   const ra_ring_plan* plan = nullptr;  // not owned; NULL: every step runs
+  bool ignore_plan = false;            // the call in progress runs every step (RA_MOD_STRICT_NAN)
   ncclComm_t comm = nullptr;
   cudaStream_t push_stream = nullptr;    // transfers this rank issues (high priority)
   cudaStream_t reduce_stream = nullptr;  // sums of dK/dV contributions this rank receives (p2p)
@@ -208,6 +218,10 @@ struct ra_ring {
   void* rpart[2] = {nullptr, nullptr};  // a remote rank's dK/dV contribution for this rank's block
   size_t stage_bytes = 0, rpart_bytes = 0;
   uint64_t* flags = nullptr;
+  // [0] abort word: set by a wait that ran out, checked by every later wait and flag store of
+  // this ring; [2..3] a 64-bit counter nothing ever advances (ra_ring_probe_wait)
+  unsigned int* guard = nullptr;
+  long long wait_cycles = 0;  // bound of one wait for a peer, in SM cycles
   struct Peer {
     void* stage[2] = {nullptr, nullptr};
     void* rpart[2] = {nullptr, nullptr};
@@ -226,6 +240,9 @@ struct ra_ring {
   std::vector<cudaEvent_t> b_events[2];  // pairs bracketing each block-kernel launch
   cudaEvent_t t_begin[2] = {nullptr, nullptr}, t_end[2] = {nullptr, nullptr};
   size_t t_used[2] = {0, 0}, b_used[2] = {0, 0};
+  std::vector<cudaEvent_t> p_events[2];  // pairs bracketing each transfer this rank issues
+  size_t p_used[2] = {0, 0};
+  double p_bytes[2] = {0, 0};            // bytes this rank sent in the last call of each direction
   int dir = 0;  // direction of the call in progress
 };
 
@@ -373,19 +390,32 @@ int block_mark(ra_ring_t* r, int dir, cudaStream_t s) {
   return 0;
 }
 
+// How long a rank waits for a peer before it gives up (the peer may simply be late: another
+// stream of work, a slow host), counted in SM cycles at 2 GHz.
+long long wait_cycles_of_ms(long long ms) {
+  if (ms < 1) ms = 1;
+  if (ms > 600000) ms = 600000;
+  return ms * 2000000LL;
+}
+
+// Brackets one outgoing transfer on the transfer stream (timing on only).
+int push_mark(ra_ring_t* r, cudaStream_t s, double bytes) {
+  if (!r->timing) return 0;
+  const int d = r->dir;
+  if (r->p_used[d] == r->p_events[d].size()) {
+    cudaEvent_t e;
+    RA_CUDA(cudaEventCreate(&e), "cudaEventCreate");
+    r->p_events[d].push_back(e);
+  }
+  RA_CUDA(cudaEventRecord(r->p_events[d][r->p_used[d]++], s), "cudaEventRecord");
+  r->p_bytes[d] += bytes;
+  return 0;
+}
+
 int launch_wait(ra_ring_t* r, cudaStream_t s, int flag_index, uint64_t target) {
   unsigned int* status = device_status_word();
   if (!status) return fail(RA_ERR_CUDA, "status word symbol not found");
-  // How long a rank waits for a peer before it gives up (the peer may simply be late: another
-  // stream of work, a slow host).  RA_RING_WAIT_MS, default 10 s; counted in SM cycles at 2 GHz.
-  static const long long max_cycles = [] {
-    const char* env = getenv("RA_RING_WAIT_MS");
-    long long ms = env ? atoll(env) : 10000;
-    if (ms < 1) ms = 1;
-    if (ms > 600000) ms = 600000;
-    return ms * 2000000LL;
-  }();
-  wait_flag_kernel<<<1, 1, 0, s>>>(r->flags + flag_index, target, status, max_cycles);
+  wait_flag_kernel<<<1, 1, 0, s>>>(r->flags + flag_index, target, status, r->guard, r->wait_cycles);
   count_launch();
   RA_CUDA(cudaGetLastError(), "wait_flag_kernel");
   return 0;
@@ -400,7 +430,7 @@ int launch_set(ra_ring_t* r, cudaStream_t s, int peer, int flag_index, uint64_t 
     list.ptr[list.n++] = r->peers[j].flags + flag_index;
   }
   if (list.n == 0) return 0;
-  set_flags_kernel<<<1, kMaxRanks, 0, s>>>(list, value);
+  set_flags_kernel<<<1, kMaxRanks, 0, s>>>(list, value, r->guard);
   count_launch();
   RA_CUDA(cudaGetLastError(), "set_flags_kernel");
   return 0;
@@ -430,16 +460,69 @@ void close_peers(ra_ring_t* r) {
   }
 }
 
+// Sizes of everything a ring call keeps in the handle, from the shape alone.
+struct RingSizes {
+  size_t o_bytes, ml_bytes;                                // forward state
+  size_t delta_b, dq_b, dk_b, dv_b, own2_dk_b, own2_dv_b;  // backward accumulators
+  bool split_b, split_h;  // the own backward block runs as two batch halves / head halves
+  int b0, h0, nb2, nh2;
+  size_t rows2;
+};
+
+RingSizes ring_sizes(const ra_shape_t* shape, int nranks) {
+  RingSizes z;
+  const size_t qrows = (size_t)shape->b * shape->h * shape->lq;
+  const size_t krows = (size_t)shape->b * shape->h * shape->lk;
+  z.o_bytes = align_up(qrows * shape->dv * 4);
+  z.ml_bytes = align_up(qrows * 4);
+  z.delta_b = align_up(qrows * 4);
+  z.dq_b = align_up(qrows * shape->dk * 4);
+  z.dk_b = align_up(krows * shape->dk * 4);
+  z.dv_b = align_up(krows * shape->dv * 4);
+  // With more than one rank the own block is computed in two parts, the first before and the
+  // second after the remote blocks: the second part runs while the last remote block's dK/dV
+  // contributions are still travelling and being summed, which would otherwise be exposed.
+  // The parts are batch halves, or head halves when there is one batch element; the second
+  // part's dK/dV go to a buffer of their own (the owner-side sums write the accumulators
+  // meanwhile) and are added at the end.
+  z.split_b = nranks > 1 && shape->b >= 2;
+  z.split_h = nranks > 1 && shape->b == 1 && shape->h >= 2;
+  {
+    // the final sum of the second part reads float4: its first row must sit on a 16-byte boundary
+    const int64_t off = ((int64_t)(z.split_b ? shape->b / 2 : 0) * shape->h + (z.split_h ? shape->h / 2 : 0)) * shape->lk;
+    if ((off * shape->dk) % 4 || (off * shape->dv) % 4) z.split_b = z.split_h = false;
+  }
+  const bool split = z.split_b || z.split_h;
+  z.b0 = z.split_b ? shape->b / 2 : 0;
+  z.h0 = z.split_h ? shape->h / 2 : 0;
+  z.nb2 = z.split_b ? shape->b - z.b0 : shape->b;
+  z.nh2 = z.split_h ? shape->h - z.h0 : shape->h;
+  z.rows2 = split ? (size_t)z.nb2 * z.nh2 * shape->lk : 0;
+  z.own2_dk_b = align_up(z.rows2 * shape->dk * 4);
+  z.own2_dv_b = align_up(z.rows2 * shape->dv * 4);
+  return z;
+}
+
 // Collective over the ring: all-gathers the IPC handles of this rank's shared buffers and maps
 // every peer's.  Runs at creation and whenever the shared buffers have been re-allocated.
+// When a rank cannot export or map a buffer (a peer that is not reachable over NVLink / PCIe
+// peer access, another node), all ranks agree on it through one more small all-gather and the
+// ring falls back to the NCCL transport as a whole: r->p2p becomes false on every rank.
+// RA_FAULT_IPC_OPEN=<rank> makes that rank report a failed mapping (host-side fault injection
+// for tests).
 int exchange_handles(ra_ring_t* r) {
   NcclApi* api = nccl_api();
   IpcBundle mine;
-  for (int i = 0; i < 2; ++i) {
-    RA_CUDA(cudaIpcGetMemHandle(&mine.stage[i], r->stage[i]), "cudaIpcGetMemHandle(stage)");
-    RA_CUDA(cudaIpcGetMemHandle(&mine.rpart[i], r->rpart[i]), "cudaIpcGetMemHandle(rpart)");
-  }
-  RA_CUDA(cudaIpcGetMemHandle(&mine.flags, r->flags), "cudaIpcGetMemHandle(flags)");
+  memset(&mine, 0, sizeof(mine));
+  int ok_local = 1;
+  for (int i = 0; i < 2 && ok_local; ++i)
+    if (cudaIpcGetMemHandle(&mine.stage[i], r->stage[i]) != cudaSuccess ||
+        cudaIpcGetMemHandle(&mine.rpart[i], r->rpart[i]) != cudaSuccess)
+      ok_local = 0;
+  if (ok_local && cudaIpcGetMemHandle(&mine.flags, r->flags) != cudaSuccess) ok_local = 0;
+  if (!ok_local) cudaGetLastError();
+  if (const char* inj = getenv("RA_FAULT_IPC_OPEN"))
+    if (atoi(inj) == r->rank) ok_local = 0;
   RA_CUDA(cudaMemcpy(r->ipc_send, &mine, sizeof(mine), cudaMemcpyHostToDevice), "cudaMemcpy");
   RA_NCCL(api->AllGather(r->ipc_send, r->ipc_recv, sizeof(mine), ncclChar, r->comm, r->push_stream), "ncclAllGather");
   RA_CUDA(cudaStreamSynchronize(r->push_stream), "cudaStreamSynchronize");
@@ -457,13 +540,28 @@ int exchange_handles(ra_ring_t* r) {
       p.flags = r->flags;
       continue;
     }
-    for (int i = 0; i < 2; ++i) {
-      RA_CUDA(cudaIpcOpenMemHandle(&p.stage[i], all[j].stage[i], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(stage)");
-      RA_CUDA(cudaIpcOpenMemHandle(&p.rpart[i], all[j].rpart[i], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(rpart)");
-    }
+    if (!ok_local) continue;
+    for (int i = 0; i < 2 && ok_local; ++i)
+      if (cudaIpcOpenMemHandle(&p.stage[i], all[j].stage[i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+          cudaIpcOpenMemHandle(&p.rpart[i], all[j].rpart[i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+        ok_local = 0;
     void* f = nullptr;
-    RA_CUDA(cudaIpcOpenMemHandle(&f, all[j].flags, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle(flags)");
+    if (ok_local && cudaIpcOpenMemHandle(&f, all[j].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) ok_local = 0;
     p.flags = (uint64_t*)f;
+    if (!ok_local) cudaGetLastError();  // clear the error state: the failure is handled below
+  }
+  // agree: one failing rank moves the whole ring to the NCCL transport
+  RA_CUDA(cudaMemcpy(r->ipc_send, &ok_local, sizeof(int), cudaMemcpyHostToDevice), "cudaMemcpy");
+  RA_NCCL(api->AllGather(r->ipc_send, r->ipc_recv, sizeof(int), ncclChar, r->comm, r->push_stream), "ncclAllGather");
+  RA_CUDA(cudaStreamSynchronize(r->push_stream), "cudaStreamSynchronize");
+  std::vector<int> oks(r->nranks, 0);
+  RA_CUDA(cudaMemcpy(oks.data(), r->ipc_recv, sizeof(int) * r->nranks, cudaMemcpyDeviceToHost), "cudaMemcpy");
+  bool all_ok = true;
+  for (int v : oks) all_ok = all_ok && v != 0;
+  if (!all_ok) {
+    close_peers(r);
+    r->peers.clear();
+    r->p2p = false;
   }
   return 0;
 }
@@ -506,7 +604,7 @@ int exchange_kv_nccl(ra_ring_t* r, const KvMessage& msg, void* stage, int to, in
 // Under a plan a transfer whose consumer has nothing visible in the block is left out, on both
 // sides: sender and receiver read the same matrix.
 bool pair_needed(const ra_ring_t* r, int q_rank, int kv_rank) {
-  return !r->plan || r->plan->need[(size_t)q_rank * r->nranks + kv_rank] != 0;
+  return !r->plan || r->ignore_plan || r->plan->need[(size_t)q_rank * r->nranks + kv_rank] != 0;
 }
 
 int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
@@ -519,9 +617,13 @@ int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
     const uint64_t need = t >= 3 ? r->epoch + t - 1 : r->epoch;
     int rc;
     if ((rc = launch_wait(r, r->push_stream, kFlagProgress + to, need))) return rc;
+    double sent = 0;
+    for (int i = 0; i < msg.n; ++i) sent += (double)msg.bytes[i];
+    if ((rc = push_mark(r, r->push_stream, sent))) return rc;
     for (int i = 0; i < msg.n; ++i)
       RA_CUDA(cudaMemcpyAsync((char*)r->peers[to].stage[slot] + msg.offset[i], msg.src[i], msg.bytes[i],
                               cudaMemcpyDeviceToDevice, r->push_stream), "cudaMemcpyAsync(peer K/V)");
+    if ((rc = push_mark(r, r->push_stream, 0))) return rc;
     return launch_set(r, r->push_stream, to, kFlagKvReady + slot, r->epoch + t);
   }
   if (t >= 2) RA_CUDA(cudaStreamWaitEvent(r->push_stream, r->ev_done[slot], 0), "cudaStreamWaitEvent");
@@ -558,6 +660,8 @@ int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
   ring->dir = dir;
   ring->t_used[dir] = 0;
   ring->b_used[dir] = 0;
+  ring->p_used[dir] = 0;
+  ring->p_bytes[dir] = 0;
   if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_begin[dir], stream), "cudaEventRecord");
   return 0;
 }
@@ -642,6 +746,12 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
   for (int d = 0; d < 2; ++d)
     if ((e = cudaEventCreate(&r->t_begin[d])) != cudaSuccess || (e = cudaEventCreate(&r->t_end[d])) != cudaSuccess)
       return bail(fail_cuda(e, "cudaEventCreate"));
+  if ((e = cudaMalloc((void**)&r->guard, 256)) != cudaSuccess || (e = cudaMemset(r->guard, 0, 256)) != cudaSuccess)
+    return bail(fail_cuda(e, "cudaMalloc(guard)"));
+  {
+    const char* env = getenv("RA_RING_WAIT_MS");  // default 10 s
+    r->wait_cycles = wait_cycles_of_ms(env ? atoll(env) : 10000);
+  }
   if (nranks > 1) {
     if (!nccl_id) return bail(fail(-34, "nccl_id is NULL with nranks > 1"));
     NcclApi* api = nccl_api();
@@ -682,6 +792,7 @@ int ra_ring_destroy(ra_ring_t* r) {
   for (int d = 0; d < 2; ++d) {
     for (cudaEvent_t ev : r->t_events[d]) cudaEventDestroy(ev);
     for (cudaEvent_t ev : r->b_events[d]) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : r->p_events[d]) cudaEventDestroy(ev);
   }
   if (r->push_stream) cudaStreamDestroy(r->push_stream);
   if (r->reduce_stream) cudaStreamDestroy(r->reduce_stream);
@@ -693,6 +804,7 @@ int ra_ring_destroy(ra_ring_t* r) {
     if (r->rpart[i]) cudaFree(r->rpart[i]);
   }
   if (r->flags) cudaFree(r->flags);
+  if (r->guard) cudaFree(r->guard);
   if (r->ipc_send) cudaFree(r->ipc_send);
   if (r->ipc_recv) cudaFree(r->ipc_recv);
   delete r;
@@ -706,6 +818,37 @@ int ra_ring_set_timing(ra_ring_t* r, int32_t on) {
   if (!r) return fail(-30, "ring handle is NULL");
   r->timing = on != 0;
   return 0;
+}
+
+int ra_ring_set_wait_ms(ra_ring_t* r, int32_t ms) {
+  if (!r) return fail(-30, "ring handle is NULL");
+  if (ms < 1) return fail(-43, "the wait bound must be at least 1 ms");
+  r->wait_cycles = wait_cycles_of_ms(ms);
+  return 0;
+}
+
+int ra_ring_probe_wait(ra_ring_t* r, void* stream) {
+  if (!r) return fail(-30, "ring handle is NULL");
+  unsigned int* status = device_status_word();
+  if (!status) return fail(RA_ERR_CUDA, "status word symbol not found");
+  // guard[2..3]: a counter that stays 0 for the life of the ring; the target is never reached
+  wait_flag_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint64_t*>(r->guard + 2), 1, status, r->guard,
+                                                     r->wait_cycles);
+  count_launch();
+  RA_CUDA(cudaGetLastError(), "wait_flag_kernel");
+  return 0;
+}
+
+int ra_ring_aborted(ra_ring_t* r) {
+  if (!r) return fail(-30, "ring handle is NULL");
+  unsigned int v = 0;
+  RA_CUDA(cudaMemcpy(&v, r->guard, sizeof(v), cudaMemcpyDeviceToHost), "cudaMemcpy");
+  return v ? 1 : 0;
+}
+
+int ra_ring_transport(const ra_ring_t* r) {
+  if (!r) return fail(-30, "ring handle is NULL");
+  return r->nranks == 1 ? 0 : (r->p2p ? 1 : 2);
 }
 
 int ra_ring_last_timing(ra_ring_t* r, int32_t backward, float* total_ms, float* exposed_ms) {
@@ -722,6 +865,23 @@ int ra_ring_last_timing(ra_ring_t* r, int32_t backward, float* total_ms, float* 
   }
   if (total_ms) *total_ms = tot;
   if (exposed_ms) *exposed_ms = exp;
+  return 0;
+}
+
+int ra_ring_last_push(ra_ring_t* r, int32_t backward, double* bytes, float* push_ms) {
+  if (!r) return fail(-30, "ring handle is NULL");
+  if (!r->timing) return fail(-35, "timing is off: call ra_ring_set_timing(ring, 1) first");
+  const int dir = backward ? 1 : 0;
+  RA_CUDA(cudaEventSynchronize(r->t_end[dir]), "cudaEventSynchronize");
+  if (r->push_stream) RA_CUDA(cudaStreamSynchronize(r->push_stream), "cudaStreamSynchronize");
+  float sum = 0.f;
+  for (size_t i = 0; i + 1 < r->p_used[dir]; i += 2) {
+    float ms = 0.f;
+    RA_CUDA(cudaEventElapsedTime(&ms, r->p_events[dir][i], r->p_events[dir][i + 1]), "cudaEventElapsedTime");
+    sum += ms;
+  }
+  if (bytes) *bytes = r->p_bytes[dir];
+  if (push_ms) *push_ms = sum;
   return 0;
 }
 
@@ -769,13 +929,14 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   p.dv = shape->dv;
   p.scale = shape->sm_scale;
 
-  const size_t rows = (size_t)shape->b * shape->h * shape->lq;
-  const size_t o_bytes = align_up(rows * shape->dv * 4), ml_bytes = align_up(rows * 4);
+  const RingSizes z = ring_sizes(shape, N);
+  const size_t o_bytes = z.o_bytes, ml_bytes = z.ml_bytes;
   RA_CUDA(ring->state.reserve(o_bytes + 2 * ml_bytes), "cudaMalloc(state)");
   p.o = (float*)ring->state.ptr;
   p.m = (float*)((char*)ring->state.ptr + o_bytes);
   p.l = (float*)((char*)ring->state.ptr + o_bytes + ml_bytes);
 
+  ring->ignore_plan = (p.mod.kinds & RA_MOD_STRICT_NAN) != 0;
   KvMessage msg = make_kv_message(shape, p.k, p.v, p.mod);
   if (N > 1 && (rc = ensure_shared(ring, msg.total, 0))) return rc;
   if ((rc = begin_call(ring, 0, stream))) return rc;
@@ -889,29 +1050,12 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   p.scale = shape->sm_scale;
   p.lse = lse;
 
-  const size_t qrows = (size_t)shape->b * shape->h * shape->lq;
-  const size_t krows = (size_t)shape->b * shape->h * shape->lk;
-  const size_t delta_b = align_up(qrows * 4), dq_b = align_up(qrows * shape->dk * 4);
-  const size_t dk_b = align_up(krows * shape->dk * 4), dv_b = align_up(krows * shape->dv * 4);
-  // With more than one rank the own block is computed in two parts, the first before and the
-  // second after the remote blocks: the second part runs while the last remote block's dK/dV
-  // contributions are still travelling and being summed, which would otherwise be exposed.
-  // The parts are batch halves, or head halves when there is one batch element; the second
-  // part's dK/dV go to a buffer of their own (the owner-side sums write the accumulators
-  // meanwhile) and are added at the end.
-  const int N_ = ring->nranks;
+  const RingSizes z = ring_sizes(shape, N);
+  const size_t delta_b = z.delta_b, dq_b = z.dq_b, dk_b = z.dk_b, dv_b = z.dv_b;
   const int esize = shape->dtype == RA_DTYPE_BF16 ? 2 : 4;
-  bool split_b = N_ > 1 && shape->b >= 2, split_h = N_ > 1 && shape->b == 1 && shape->h >= 2;
-  {
-    // the final sum of the second part reads float4: its first row must sit on a 16-byte boundary
-    const int64_t off = ((int64_t)(split_b ? shape->b / 2 : 0) * shape->h + (split_h ? shape->h / 2 : 0)) * shape->lk;
-    if ((off * shape->dk) % 4 || (off * shape->dv) % 4) split_b = split_h = false;
-  }
-  const bool split = split_b || split_h;
-  const int b0 = split_b ? shape->b / 2 : 0, h0 = split_h ? shape->h / 2 : 0;
-  const int nb2 = split_b ? shape->b - b0 : shape->b, nh2 = split_h ? shape->h - h0 : shape->h;
-  const size_t rows2 = split ? (size_t)nb2 * nh2 * shape->lk : 0;
-  const size_t own2_dk_b = align_up(rows2 * shape->dk * 4), own2_dv_b = align_up(rows2 * shape->dv * 4);
+  const bool split_b = z.split_b, split_h = z.split_h, split = split_b || split_h;
+  const int b0 = z.b0, h0 = z.h0, nb2 = z.nb2, nh2 = z.nh2;
+  const size_t rows2 = z.rows2, own2_dk_b = z.own2_dk_b, own2_dv_b = z.own2_dv_b;
   RA_CUDA(ring->grads.reserve(delta_b + dq_b + dk_b + dv_b + own2_dk_b + own2_dv_b), "cudaMalloc(grads)");
   char* g = (char*)ring->grads.ptr;
   float* delta = (float*)g;
@@ -939,7 +1083,8 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   p.dk = dk_acc;
   p.dv = dv_acc;
   bool direct = false;
-  if (N == 1 && current_impl() != RA_IMPL_SIMT) {
+  ring->ignore_plan = (p.mod.kinds & RA_MOD_STRICT_NAN) != 0;
+  if (N == 1 && current_impl() != RA_IMPL_SIMT && !(p.mod.kinds & RA_MOD_STRICT_NAN)) {
     p.dk_out = tv(dk);
     p.dv_out = tv(dv);
     direct = tc_bwd_unsupported_reason(p, shape->dtype) == nullptr;
@@ -981,9 +1126,9 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       if ((rc = run_bwd_block(first, shape->dtype, stream))) return rc;
       if ((rc = block_mark(ring, 1, stream))) return rc;
       if ((rc = step_done(ring, 0, stream))) return rc;
-      if (N > 1 && ring->p2p) {  // the sums of received contributions start after the own block's
+      if (N > 1) {  // the sums of received contributions start after the accumulators were cleared and the own block's part added
         RA_CUDA(cudaEventRecord(ring->ev_step0, stream), "cudaEventRecord");
-        RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_step0, 0), "cudaStreamWaitEvent");
+        if (ring->p2p) RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_step0, 0), "cudaStreamWaitEvent");
       }
       continue;
     }
@@ -997,13 +1142,14 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       if ((rc = wait_kv(ring, t, stream))) return rc;
       // this step's contribution to the remote block's dK/dV, built from zero
       if (t >= 3) RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
+      // this step's contribution is built from nothing: the kernel stores instead of adding
       p.dk = (float*)ring->part[slot].ptr;
       p.dv = (float*)((char*)ring->part[slot].ptr + dk_b);
-      RA_CUDA(cudaMemsetAsync(ring->part[slot].ptr, 0, dk_b + dv_b, stream), "cudaMemsetAsync");
-      count_launch();
+      p.overwrite = 1;
       if ((rc = block_mark(ring, 1, stream))) return rc;
       if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
       if ((rc = block_mark(ring, 1, stream))) return rc;
+      p.overwrite = 0;
     }
     if ((rc = step_done(ring, t, stream))) return rc;
     if (compute) {
@@ -1016,8 +1162,10 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
         // the owner's rpart[slot] is free once it has summed the contribution of step t-2
         const uint64_t need = t >= 3 ? ring->epoch + t - 1 : ring->epoch;
         if ((rc = launch_wait(ring, ring->push_stream, kFlagAdded + owner, need))) return rc;
+        if ((rc = push_mark(ring, ring->push_stream, (double)(dk_b + dv_b)))) return rc;
         RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
                                 cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
+        if ((rc = push_mark(ring, ring->push_stream, 0))) return rc;
         if ((rc = launch_set(ring, ring->push_stream, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
         RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
       }
@@ -1031,6 +1179,8 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
     }
     if (receive) {
+      // NCCL transport: the sum runs on the transfer stream, which has not seen the own block yet
+      if (!ring->p2p) RA_CUDA(cudaStreamWaitEvent(add_stream, ring->ev_step0, 0), "cudaStreamWaitEvent");
       e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot], (int64_t)((dk_b + dv_b) / 4), add_stream);
       if (e != cudaSuccess) return fail_cuda(e, "add");
     }
@@ -1047,8 +1197,7 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     BwdParams second = sub_problem(p, esize, b0, nb2, h0, nh2);
     second.dk = own2_dk;
     second.dv = own2_dv;
-    RA_CUDA(cudaMemsetAsync(own2_dk, 0, own2_dk_b + own2_dv_b, stream), "cudaMemsetAsync");
-    count_launch();
+    second.overwrite = 1;  // built from nothing: no clearing pass
     if ((rc = block_mark(ring, 1, stream))) return rc;
     if ((rc = run_bwd_block(second, shape->dtype, stream))) return rc;
     if ((rc = block_mark(ring, 1, stream))) return rc;
@@ -1065,6 +1214,42 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       (e = launch_cast_from_f32(shape->b, shape->h, shape->lk, shape->dv, dv_acc, tv(dv), shape->dtype, stream)) != cudaSuccess)
     return fail_cuda(e, "cast");
   return end_call(ring, 1, stream);
+}
+
+int ra_ring_reserve(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod_t* mod, int32_t backward) {
+  int rc;
+  if (!ring) return fail(-30, "ring handle is NULL");
+  if ((rc = check_shape(shape))) return rc;
+  int dev = -1;
+  RA_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev != ring->device) return fail(-31, "ring was created on device %d but device %d is current", ring->device, dev);
+  const int N = ring->nranks;
+  const RingSizes z = ring_sizes(shape, N);
+  // size of one K/V block message: only which per-token arrays exist matters, not where they are
+  ModParams m;
+  memset(&m, 0, sizeof(m));
+  if (mod) {
+    m.kv_pos = mod->kv_pos;
+    m.kv_seg = mod->kv_seg;
+    m.kv_pre = mod->kv_prefix;
+  }
+  const TensorView none{nullptr, 0, 0, 0};
+  const KvMessage msg = make_kv_message(shape, none, none, m);
+  RA_CUDA(ring->state.reserve(z.o_bytes + 2 * z.ml_bytes), "cudaMalloc(state)");
+  if (backward) {
+    RA_CUDA(ring->grads.reserve(z.delta_b + z.dq_b + z.dk_b + z.dv_b + z.own2_dk_b + z.own2_dv_b), "cudaMalloc(grads)");
+    if (N > 1)
+      for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(z.dk_b + z.dv_b), "cudaMalloc(part)");
+  }
+  if (N > 1 && (rc = ensure_shared(ring, msg.total, backward ? z.dk_b + z.dv_b : 0))) return rc;
+  // the block kernels take their tile summaries from a stream-ordered pool that keeps what it
+  // was given: give it this shape's worth now
+  void* tmp = nullptr;
+  const size_t meta_bytes = (size_t)shape->b * ((shape->lq + 127) / 128 + (shape->lk + 127) / 128) * sizeof(TileMeta);
+  RA_CUDA(scratch_alloc(&tmp, meta_bytes, ring->push_stream), "scratch pool");
+  RA_CUDA(cudaFreeAsync(tmp, ring->push_stream), "cudaFreeAsync");
+  RA_CUDA(cudaStreamSynchronize(ring->push_stream), "cudaStreamSynchronize");
+  return 0;
 }
 
 int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod_t* mod, void* stream_,

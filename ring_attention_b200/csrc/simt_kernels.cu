@@ -495,6 +495,25 @@ __global__ void add_f32_kernel(float* __restrict__ dst, const float* __restrict_
   }
 }
 
+__global__ void strict_nan_kernel(int lq, int lk, int dk_dim, int dv_dim, const float* __restrict__ lse,
+                                  float* __restrict__ dq, float* __restrict__ dk, float* __restrict__ dv) {
+  const int64_t bh = blockIdx.x;
+  const float* L = lse + bh * lq;
+  const float nan = __int_as_float(0x7fc00000);
+  int any = 0;
+  for (int i = threadIdx.x; i < lq; i += blockDim.x)
+    if (L[i] == -INFINITY) any = 1;
+  any = __syncthreads_or(any);
+  if (!any) return;
+  float* dq_bh = dq + bh * lq * dk_dim;
+  for (int64_t e = threadIdx.x; e < (int64_t)lq * dk_dim; e += blockDim.x)
+    if (L[e / dk_dim] == -INFINITY) dq_bh[e] = nan;
+  float* dk_bh = dk + bh * lk * dk_dim;
+  for (int64_t e = threadIdx.x; e < (int64_t)lk * dk_dim; e += blockDim.x) dk_bh[e] = nan;
+  float* dv_bh = dv + bh * lk * dv_dim;
+  for (int64_t e = threadIdx.x; e < (int64_t)lk * dv_dim; e += blockDim.x) dv_bh[e] = nan;
+}
+
 template <typename T, int D_PAD>
 cudaError_t launch_fwd(const FwdParams& p, cudaStream_t s) {
   size_t smem = sizeof(float) * (2 * 64 * LDS + 64 * LDP + 64 * D_PAD);
@@ -577,6 +596,13 @@ cudaError_t launch_cast_from_f32(int b, int h, int len, int d, const float* src,
     cast_kernel<float><<<grid, 256, 0, s>>>(b, h, len, d, src, dst);
   else
     cast_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(b, h, len, d, src, dst);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_strict_nan(int b, int h, int lq, int lk, int dk_dim, int dv_dim, const float* lse, float* dq,
+                              float* dk, float* dv, cudaStream_t s) {
+  strict_nan_kernel<<<b * h, 512, 0, s>>>(lq, lk, dk_dim, dv_dim, lse, dq, dk, dv);
   count_launch();
   return cudaGetLastError();
 }

@@ -83,6 +83,29 @@ class Ring:
         check(lib.ra_ring_last_block_ms(self.handle, int(backward), C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
+    def last_push(self, backward: bool):
+        """(bytes this rank pushed to peers, device ms of those copies) in the last forward / backward ring call."""
+        nbytes, ms = C.c_double(), C.c_float()
+        check(lib.ra_ring_last_push(self.handle, int(backward), C.byref(nbytes), C.byref(ms)))
+        return nbytes.value, ms.value
+
+    @property
+    def transport(self) -> str:
+        """"none" (ring of one), "p2p" (peer copies over CUDA IPC) or "nccl"."""
+        return {0: "none", 1: "p2p", 2: "nccl"}[lib.ra_ring_transport(self.handle)]
+
+    def set_wait_ms(self, ms: int) -> None:
+        """Bound of one wait for a peer; a wait that runs out aborts the ring (see `aborted`)."""
+        check(lib.ra_ring_set_wait_ms(self.handle, int(ms)))
+
+    @property
+    def aborted(self) -> bool:
+        """True once a wait for a peer has run out: results since then are undefined and the
+        ring must be destroyed and created again on every rank."""
+        r = lib.ra_ring_aborted(self.handle)
+        check(min(r, 0))
+        return r == 1
+
     def destroy(self) -> None:
         if getattr(self, "_h", None) is not None:
             lib.ra_ring_destroy(self._h)

@@ -81,10 +81,15 @@ class ScoreMod:
     prefix_mask.  Segment and prefix masking switch on when those arrays are passed.
     """
 
-    def __init__(self, causal: bool = False, alibi_slopes: Optional[torch.Tensor] = None, window: int = 0):
+    def __init__(self, causal: bool = False, alibi_slopes: Optional[torch.Tensor] = None, window: int = 0,
+                 strict_nan: bool = False):
         self.causal = bool(causal)
         self.alibi_slopes = alibi_slopes
         self.window = int(window)
+        # True: a query row that sees no key poisons dQ of that row and dK, dV of its whole
+        # (batch, head) with NaN, as the reference's arithmetic does (ring.py:146); False
+        # (default): such rows contribute nothing to the gradients
+        self.strict_nan = bool(strict_nan)
 
     def kinds(self, q_kwargs: dict, kv_kwargs: dict) -> int:
         k = 0
@@ -98,6 +103,8 @@ class ScoreMod:
             k |= _lib.RA_MOD_ALIBI
         if self.window:
             k |= _lib.RA_MOD_WINDOW
+        if self.strict_nan:
+            k |= _lib.RA_MOD_STRICT_NAN
         return k
 
     def __call__(self, q_segment_ids=None, kv_segment_ids=None, q_positions=None, kv_positions=None,
@@ -402,6 +409,24 @@ def make_ring_plan(q: torch.Tensor, k: torch.Tensor, axis_name, bias_fn, bias_q_
     return RingPlan(ring, handle)
 
 
+def reserve(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, axis_name,
+            bias_kv_kwargs: Optional[dict] = None, backward: bool = True) -> None:
+    """Allocates everything the ring keeps for calls with these shard shapes ([b, l, h, d]) ahead
+    of time (`ra_ring_reserve`): afterwards `ring_attention` calls of the same or a smaller shape
+    neither allocate inside the library nor synchronise the device.  Every rank must call it."""
+    ring = resolve_axis(axis_name)
+    b, lq, h, dk = q.shape
+    m = None
+    if bias_kv_kwargs:
+        # only which kv-side arrays exist matters (they travel with K/V); the pointers are not read
+        m = RaScoreMod()
+        for field, key in (("kv_pos", "kv_positions"), ("kv_seg", "kv_segment_ids"), ("kv_prefix", "kv_prefix_mask")):
+            if bias_kv_kwargs.get(key) is not None:
+                setattr(m, field, bias_kv_kwargs[key].data_ptr())
+    sh = _shape(b, h, lq, k.shape[1], dk, v.shape[3], _dtype_code(q), 1.0)
+    check(lib.ra_ring_reserve(ring.handle, C.byref(sh), C.byref(m) if m is not None else None, int(backward)))
+
+
 class _UsePlan:
     """Applies a plan to a ring handle for the calls inside the `with` block."""
 
@@ -423,6 +448,8 @@ class _RingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, ring, sm_scale, bias_fn, q_kwargs, kv_kwargs, impl, plan):
         q, k, v = _blhd(q), _blhd(k), _blhd(v)
+        if ring.size > 1:  # K/V blocks travel as flat messages: slices of a packed projection are copied once
+            k, v = k.contiguous(), v.contiguous()
         fused = bias_fn is None or isinstance(bias_fn, ScoreMod)
         check(lib.ra_set_impl(impl))
         fwd = _fused_fwd if fused else _host_fwd

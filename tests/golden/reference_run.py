@@ -5,8 +5,10 @@ NumPy stand-in of jax_on_numpy.py, with one thread per virtual device, in float6
 by the reference's functions themselves: `ring_attention` / `ring_self_attention`, the custom-VJP
 pair `_ring_attention_fwd` / `_ring_attention_bwd`, `_fwd_block` / `_bwd_block`, `_rotate_block`
 and the built-in mask builder; with `block_impl="pallas"` also the kernels of ring_kernel.py,
-through the stand-in's interpreter of the Pallas calls they make.  Needs the reference checkout
-(REFERENCE_DIR, default /root/reference); nothing here ships with the product.
+through the stand-in's interpreter of the Pallas calls they make.  Needs the reference checkout:
+the directory named by the environment variable REFERENCE_DIR, else a checkout called
+`reference` beside this repository; without either the callers skip.  Nothing here ships with
+the product.
 """
 from __future__ import annotations
 
@@ -21,7 +23,8 @@ sys.path.insert(0, HERE)
 
 import jax_on_numpy as standin  # noqa: E402
 
-REFERENCE_DIR = os.environ.get("REFERENCE_DIR", "/root/reference")
+REFERENCE_DIR = os.environ.get("REFERENCE_DIR") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
 
 
 def available() -> bool:

@@ -129,9 +129,10 @@ def test_ring_attention_bias_fn_nan_pattern(seed, lq, lk, h, d, dtype):
               bias_kv_kwargs={"kv_segment_ids": to_dev(kseg, torch.int32)})
     ref = O.mha(q, k, v, bias)
     rq, rk, rv = O.mha_grads(q, k, v, do, bias)
-    # dense-tile path (reference NaN semantics), then the compiled-in segment mask, whose
-    # backward gives rows that saw no key a zero contribution instead of NaN
-    for fn, nan in ((bias_fn, "match"), (ra().ScoreMod(), "finite")):
+    # dense-tile path (reference NaN semantics); the compiled-in segment mask, whose backward by
+    # default gives rows that saw no key a zero contribution instead of NaN; and the same mask
+    # with strict_nan, which reproduces the reference's NaN pattern (ring.py:146, ring_test.py:273)
+    for fn, nan in ((bias_fn, "match"), (ra().ScoreMod(), "finite"), (ra().ScoreMod(strict_nan=True), "match")):
         out, dq, dk, dv = _grads(lambda a, b, c: ra().ring_attention(a, b, c, "sp", bias_fn=fn, block_impl="simt", **kw),
                                  tq, tk, tv, tdo)
         check_close(out, ref, dtype, "out")
@@ -201,6 +202,13 @@ def test_score_mod_variants_match_dense_bias(mod, dtype):
     check_close(dq, rq, dtype, "dq", 2e-5, nan="finite")
     check_close(dk, rk, dtype, "dk", 2e-5, nan="finite")
     check_close(dv, rv, dtype, "dv", 2e-5, nan="finite")
+    # the same call with the reference's NaN semantics switched on: the pattern must match exactly
+    sm.strict_nan = True
+    out, dq, dk, dv = _grads(lambda a, b_, c: ra().ring_attention(a, b_, c, "sp", bias_fn=sm, bias_q_kwargs=qkw,
+                                                                 bias_kv_kwargs=kkw, block_impl="simt"), tq, tk, tv, tdo)
+    check_close(dq, rq, dtype, "dq strict", 2e-5)
+    check_close(dk, rk, dtype, "dk strict", 2e-5)
+    check_close(dv, rv, dtype, "dv strict", 2e-5)
 
 
 @pytest.mark.parametrize("name", list(G.CASES))

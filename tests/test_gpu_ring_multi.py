@@ -29,6 +29,8 @@ def _worker(rank, world, port, case, q_out):
         dtype, lq, lk, h, d, mask, impl = case
         if "nccl" in mask:  # the NCCL send/recv transport instead of the default peer copies
             os.environ["RA_TRANSPORT"] = "nccl"
+        if "ipcfail" in mask:  # host-side fault injection: rank 1 reports that it could not map its peers' buffers
+            os.environ["RA_FAULT_IPC_OPEN"] = "1"
         dtype = getattr(torch, dtype)
         nb = 1 if "b1" in mask else 2  # one batch element: the backward splits its own block by heads, or not at all
         q, k, v, do, rng = make_inputs(5, nb, lq, lk, h, d, dtype)
@@ -57,8 +59,13 @@ def _worker(rank, world, port, case, q_out):
             kkw = {"kv_positions": T(kpos[:, sk]), "kv_segment_ids": T(seg[:, :lk][:, sk]) if use_seg else None}
         if mask == "callable":
             pass
-        with ra.Mesh((1, world), ("dp", "sp")):
+        with ra.Mesh((1, world), ("dp", "sp")) as mesh:
+            # every rank ends up on the same transport; one rank that cannot map moves the whole ring to NCCL
+            want_transport = "nccl" if ("nccl" in mask or "ipcfail" in mask) else "p2p"
+            assert mesh.ring("sp").transport == want_transport, mesh.ring("sp").transport
             tq, tk, tv = (to_dev(x, dtype).requires_grad_(True) for x in (q[:, sq], k[:, sk], v[:, sk]))
+            if "reserve" in mask:  # buffers and handle exchange ahead of the first call
+                ra.reserve(tq, tk, tv, "sp", bias_kv_kwargs=kkw)
             plan = None
             if "plan" in mask:  # leave out the ring steps whose block the mask empties
                 plan = ra.make_ring_plan(tq, tk, "sp", fn, qkw, kkw)
@@ -78,6 +85,8 @@ def _worker(rank, world, port, case, q_out):
                                         block_impl=impl, plan=plan)
                 out.backward(to_dev(do[:, sq], dtype))
             torch.cuda.synchronize()
+            # no bounded wait ran out, inside a kernel or for a peer
+            assert ra.device_status() == 0 and not mesh.ring("sp").aborted
         ref = O.mha(q, k, v, bias)
         rq, rk, rv = O.mha_grads(q, k, v, do, bias)
         check_close(out, ref[:, sq], dtype, "out")
@@ -106,6 +115,8 @@ CASES = [
     ("bfloat16", 2048, 2048, 2, 128, "causal+window256+plan", "tcgen05"),
     ("bfloat16", 4096, 4096, 2, 128, "causal+window300+zigzag+plan", "tcgen05"),
     ("float32", 512, 512, 2, 32, "causal+window100+plan+nccl", "simt"),
+    ("bfloat16", 2048, 2048, 2, 128, "causal+zigzag+ipcfail", "tcgen05"),
+    ("bfloat16", 2048, 2048, 2, 128, "causal+seg+zigzag+reserve", "tcgen05"),
 ]
 
 

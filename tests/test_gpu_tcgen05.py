@@ -109,6 +109,14 @@ def test_score_mods_forward(mod, layout):
     check_close(dq, rq, BF, "dq", nan="finite")
     check_close(dk, rk, BF, "dk", nan="finite")
     check_close(dv, rv, BF, "dv", nan="finite")
+    # with the reference's NaN semantics switched on the NaN pattern matches exactly (ring.py:146)
+    sm.strict_nan = True
+    out, dq, dk, dv = _grads(lambda a, b_, c: ra().ring_attention(a, b_, c, "sp", bias_fn=sm, bias_q_kwargs=qkw,
+                                                                 bias_kv_kwargs=kkw, block_impl="tcgen05"), tq, tk, tv, tdo)
+    _status_clean()
+    check_close(dq, rq, BF, "dq strict")
+    check_close(dk, rk, BF, "dk strict")
+    check_close(dv, rv, BF, "dv strict")
 
 
 @pytest.mark.parametrize("seed,lq,lk,h,d", [(1, 128, 2048, 2, 128), (3, 2048, 128, 2, 128), (3, 2048, 2048, 4, 128),
