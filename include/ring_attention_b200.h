@@ -278,15 +278,17 @@ int ra_ring_use_plan(ra_ring_t* ring, const ra_ring_plan_t* plan);
 int ra_ring_rotate(ra_ring_t* ring, int32_t n, const void* const* src, void* const* dst,
                    const int64_t* nbytes, void* stream);
 
-/* Milliseconds the compute stream spent blocked on transfers during the last forward
- * (backward == 0) or backward (backward != 0) ring call of this handle, and the total device
- * time of that call; both need ra_ring_set_timing(ring, 1) and synchronise on the call's end
- * when read. */
+/* Milliseconds this rank's block kernels were held up by transfers during the last forward
+ * (backward == 0) or backward (backward != 0) ring call of this handle: the time a compute lane
+ * waited for a K/V block or for the final contribution sums while no block kernel of the rank
+ * was running.  Also the total device time of that call.  Both need ra_ring_set_timing(ring, 1)
+ * and synchronise on the call's end when read. */
 int ra_ring_set_timing(ra_ring_t* ring, int32_t on);
 int ra_ring_last_timing(ra_ring_t* ring, int32_t backward, float* total_ms, float* exposed_comm_ms);
-/* Device time of the block kernels (ra_fwd_block / ra_bwd_block work) launched by the last
- * forward (backward == 0) or backward (backward != 0) ring call of this handle, summed over
- * its steps, and how many there were.  Timing must be on; the two directions are kept
+/* Device time during which block kernels (ra_fwd_block / ra_bwd_block work) of the last
+ * forward (backward == 0) or backward (backward != 0) ring call of this handle were running
+ * (adjacent steps run on two streams and overlap: the union is taken), and how many launches
+ * there were.  Timing must be on; the two directions are kept
  * apart so that a forward + backward step can be queried once, after it ended. */
 int ra_ring_last_block_ms(ra_ring_t* ring, int32_t backward, float* block_ms, int32_t* launches);
 /* Peer-copy transport: bytes this rank pushed to other ranks (K/V blocks, and dK/dV

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libring_attention_b200.so")
+# RA_LIB_PATH: load a library built elsewhere (another build of the same sources) instead of the in-tree one
+LIB_PATH = os.environ.get("RA_LIB_PATH") or os.path.join(_HERE, "libring_attention_b200.so")
 
 RA_DTYPE_F32, RA_DTYPE_BF16 = 0, 1
 RA_MOD_CAUSAL, RA_MOD_SEGMENT, RA_MOD_PREFIX, RA_MOD_ALIBI, RA_MOD_WINDOW, RA_MOD_DENSE = 1, 2, 4, 8, 16, 32

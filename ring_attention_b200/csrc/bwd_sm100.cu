@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   const int hh = bh % p.h, bb = bh / p.h;
   const uint32_t kinds = p.mod.kinds;
   const bool masked = (kinds & kMetaKinds) != 0;  // the tile summaries are read
+  const bool dense = (kinds & RA_MOD_DENSE) != 0;  // every tile takes the in-TMEM pass (it adds the bias tile)
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   // tiles before the diagonal, other documents) costs one load latency per 32 tiles.
   constexpr int kMixedBit = 1 << 16, kContigBit = 1 << 17, kTileIdx = kMixedBit - 1;
   auto next_active = [&](int i) -> int {
-    if (!masked) return i < P.n_q_tiles ? i : P.n_q_tiles;
+    if (!masked) return i < P.n_q_tiles ? (i | (dense ? kMixedBit : 0)) : P.n_q_tiles;
     for (; i < P.n_q_tiles; i += 32) {
       const int t = i + lane;
       int cls = 0;  // 0 skip, 1 all visible, 2 mixed; +4 contiguous positions
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       if (vote) {
         const int first = __ffs(vote) - 1;
         const int c = __shfl_sync(0xffffffffu, cls, first);
-        return (i + first) | ((c & 3) == 2 ? kMixedBit : 0) | ((c & 4) ? kContigBit : 0);
+        return (i + first) | (((c & 3) == 2 || dense) ? kMixedBit : 0) | ((c & 4) ? kContigBit : 0);
       }
     }
     return P.n_q_tiles;
@@ -424,7 +425,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           fixup_scores_tmem<false>(tmem_S + lane_off + g * 64, 64, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
                                    p.mod.window, alibi_over_scale, kpos, kseg, kpre,
                                    p.mod.q_pos ? p.mod.q_pos + q0 : nullptr, p.mod.q_seg ? p.mod.q_seg + q0 : nullptr,
-                                   p.mod.q_pre ? p.mod.q_pre + q0 : nullptr, q0_cur + g * 64, (e_cur & kContigBit) != 0);
+                                   p.mod.q_pre ? p.mod.q_pre + q0 : nullptr, q0_cur + g * 64, (e_cur & kContigBit) != 0,
+                                   dense ? p.mod.bias + (int64_t)bb * p.mod.bsb + (int64_t)hh * p.mod.bsh +
+                                               ((int64_t)i * kTileRows + g * 64) * p.mod.bsq + kv_row
+                                         : nullptr,
+                                   p.mod.bsq, 1.f / p.scale);
         }
         tmem_ld32(tmem_S + lane_off + g * 64, sv[0]);
         tmem_ld32(tmem_S + lane_off + g * 64 + 32, sv[1]);
@@ -447,8 +452,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           for (int e = 0; e < 4; ++e) {
             const int c = c4 * 4 + e;
             // a masked pair (-inf) gives exp2(-inf) = 0; the clamp keeps a row whose L is -inf
-            // (it saw no key) from turning that into exp2(-inf + inf)
-            const float neg_l2 = fminf(-l4[e] * kLog2e, 1e30f);
+            // (it saw no key) from turning that into exp2(-inf + inf).  With a dense bias tile
+            // the reference's arithmetic is kept as it is (ring.py:146): such a row gives NaN.
+            const float neg_l2 = dense ? -l4[e] * kLog2e : fminf(-l4[e] * kLog2e, 1e30f);
             pf[c] = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, neg_l2));
           }
         }
@@ -634,7 +640,9 @@ const char* tc_bwd_unsupported_reason(const BwdParams& p, int dtype) {
   if (p.dk_dim != p.dv_dim || (p.dk_dim != 64 && p.dk_dim != 128)) return "head dims must be equal and 64 or 128";
   if (p.lq % kTileRows || p.lk % kTileRows) return "lq and lk must be multiples of 128";
   if (p.lq / kTileRows > kMaxTiles || p.lk / kTileRows > kMaxTiles) return "more than 4096 tiles along one axis";
-  if (p.mod.kinds & RA_MOD_DENSE) return "a dense bias tile is served by the CUDA-core kernels";
+  if ((p.mod.kinds & RA_MOD_DENSE) && ((p.mod.bsb % 4) || (p.mod.bsh % 4) || (p.mod.bsq % 4) ||
+                                       (reinterpret_cast<uintptr_t>(p.mod.bias) & 15)))
+    return "the dense bias needs a 16-byte aligned base and strides that are multiples of 4 floats";
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.dout))
     return "q/k/v/dout need 16-byte aligned base and strides";
   if ((reinterpret_cast<uintptr_t>(p.lse) & 15) || (reinterpret_cast<uintptr_t>(p.delta) & 15) ||

@@ -66,8 +66,11 @@ struct BwdParams {
 // Launchers implemented in the .cu files.  Each returns a cudaError_t.
 cudaError_t simt_fwd_block(const FwdParams& p, int dtype, cudaStream_t s);
 cudaError_t simt_bwd_block(const BwdParams& p, int dtype, cudaStream_t s);
-cudaError_t launch_finalize(int b, int h, int lq, int dv, const float* o, const float* m,
-                            const float* l, TensorView out, int dtype, float* lse, cudaStream_t s);
+// out = o / l, L = m + log l (ring.py:134-135).  With o2 != NULL the two carried states are
+// merged first, as one more online-softmax update (ring.py:63-75) would.
+cudaError_t launch_finalize(int b, int h, int lq, int dv, const float* o, const float* m, const float* l,
+                            const float* o2, const float* m2, const float* l2, TensorView out, int dtype,
+                            float* lse, cudaStream_t s);
 cudaError_t launch_delta(int b, int h, int lq, int dv, TensorView out, TensorView dout, int dtype,
                          float* delta, cudaStream_t s);
 cudaError_t launch_cast_from_f32(int b, int h, int len, int d, const float* src, TensorView dst,

@@ -31,6 +31,12 @@ using namespace ptx;
 constexpr int kFwdThreads = 320;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8
+// Of every 16 column pairs of the softmax, how many get their exponentials from the polynomial
+// on the FMA pipe (the others use ex2 on the special-function unit).
+#ifndef RA_FWD_POLY_PAIRS
+#define RA_FWD_POLY_PAIRS 5
+#endif
+constexpr int kPolyPairs = RA_FWD_POLY_PAIRS;
 
 struct FwdTcParams {
   CUtensorMap map_q, map_k, map_v;
@@ -92,6 +98,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
   // query tiles are left out.  Every thread classifies its share of the tiles (one round of
   // loads for up to 320 tiles), then warp 0 compacts the classes in order.
   const bool masked = (kinds & kMetaKinds) != 0;
+  const bool dense = (kinds & RA_MOD_DENSE) != 0;  // every visited tile takes the in-TMEM pass (it adds the bias tile)
   if (masked) {
     const TileMeta mq0 = P.meta_q[bb * P.n_q_tiles + qt0];
     const TileMeta mq1 = P.meta_q[bb * P.n_q_tiles + qt0 + (ntile - 1)];
@@ -99,7 +106,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
       const TileMeta mk = P.meta_kv[bb * P.n_kv_tiles + j];
       const int c0 = classify_tiles(kinds, p.mod.window, mq0, mk);
       const int c1 = ntile == 2 ? classify_tiles(kinds, p.mod.window, mq1, mk) : 0;
-      const uint32_t code = (c0 != 1 ? 1u : 0u) | (c1 != 1 ? 2u : 0u) | (mk.pos_contig ? 4u : 0u);
+      const uint32_t code = ((c0 != 1 || dense) ? 1u : 0u) | ((c1 != 1 || dense) ? 2u : 0u) | (mk.pos_contig ? 4u : 0u);
       codes[j] = ((c0 != 0) || (c1 != 0)) ? (uint8_t)(0x80u | code) : (uint8_t)0;  // bit 7: visited
     }
     __syncthreads();
@@ -109,7 +116,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
     for (int base = 0; base < P.n_kv_tiles; base += 32) {
       const int j = base + lane;
       bool active = j < P.n_kv_tiles;
-      uint32_t code = 0;
+      uint32_t code = dense ? 3u : 0u;
       if (active && masked) {
         code = codes[j] & 0x7u;
         active = (codes[j] & 0x80u) != 0;
@@ -252,7 +259,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         fixup_scores_tmem<true>(tmem_S[t] + lane_off, kTileRows, need_mask ? kinds : (kinds & RA_MOD_ALIBI),
                                 p.mod.window, alibi_over_scale, qpos, qseg, qpre,
                                 p.mod.kv_pos ? p.mod.kv_pos + kv0 : nullptr, p.mod.kv_seg ? p.mod.kv_seg + kv0 : nullptr,
-                                p.mod.kv_pre ? p.mod.kv_pre + kv0 : nullptr, k0, kv_contig);
+                                p.mod.kv_pre ? p.mod.kv_pre + kv0 : nullptr, k0, kv_contig,
+                                dense ? p.mod.bias + (int64_t)bb * p.mod.bsb + (int64_t)hh * p.mod.bsh +
+                                            (int64_t)q_row * p.mod.bsq + (int64_t)j * kTileRows
+                                      : nullptr,
+                                1, 1.f / p.scale);
       }
       uint32_t r[4][32];
 #pragma unroll
@@ -271,11 +282,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
             r[c][e] = __float_as_uint(fmaf(slope2, (float)(c * 32 + e), fmaf(__uint_as_float(r[c][e]), scale2, r_i)));
         sc = 1.f;
       }
-      float mx = -INFINITY;  // raw scores; the scale is positive, so it commutes with max
+      // raw scores; the scale is positive, so it commutes with max.  Four independent chains of
+      // three-input maxima instead of one chain of 128 dependent operations.
+      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[c][e]));
+        for (int e = 0; e < 32; e += 2) mxa[c] = max3(mxa[c], __uint_as_float(r[c][e]), __uint_as_float(r[c][e + 1]));
+      const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
       const float m_new = fmaxf(m_true, mx * sc);
       m_true = m_new;
       const bool need = (m_new > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && m_new != -INFINITY);
@@ -297,20 +311,36 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         }
       }
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      float sum = 0.f;
+      // p = 2^(s * sc - m) on pairs of columns: the first kPolyPairs of every 16 pairs take the
+      // polynomial on the FMA pipe, the rest the special-function unit, so that the two pipes
+      // finish together; one packed sum per 32-column chunk
+      const uint64_t sc2 = pack2(sc, sc), nm2 = pack2(neg_m, neg_m);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(r[c][2 * e]), sc, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(r[c][2 * e + 1]), sc, neg_m));
-          sum += p0 + p1;
+          const uint64_t x2 = fma2(pack2(__uint_as_float(r[c][2 * e]), __uint_as_float(r[c][2 * e + 1])), sc2, nm2);
+          float p0, p1;
+          if (e < kPolyPairs) {
+            exp2_poly2(x2, p0, p1);
+          } else {
+            float x0, x1;
+            unpack2(x2, x0, x1);
+            p0 = ex2(x0);
+            p1 = ex2(x1);
+          }
+          sum2[c] = add2(sum2[c], pack2(p0, p1));
           pk[e] = pack_bf16(p0, p1);
         }
         tmem_st16(tmem_S[t] + lane_off + c * 16, pk);
       }
-      l_run += sum;
+      {
+        float s0, s1;
+        unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), s0, s1);
+        l_run += s0 + s1;
+      }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bars[P_FULL0 + t]);
@@ -575,7 +605,9 @@ const char* tc_fwd_unsupported_reason(const FwdParams& p, int dtype) {
   if (p.dk != p.dv || (p.dk != 64 && p.dk != 128)) return "head dims must be equal and 64 or 128";
   if (p.lq % kTileRows || p.lk % kTileRows) return "lq and lk must be multiples of 128";
   if (p.lq / kTileRows > kMaxTiles || p.lk / kTileRows > kMaxTiles) return "more than 4096 tiles along one axis";
-  if (p.mod.kinds & RA_MOD_DENSE) return "a dense bias tile is served by the CUDA-core kernels";
+  if ((p.mod.kinds & RA_MOD_DENSE) &&
+      ((reinterpret_cast<uintptr_t>(p.mod.bias) & 15) || (p.mod.bsb % 4) || (p.mod.bsh % 4) || (p.mod.bsq % 4)))
+    return "the dense bias needs a 16-byte aligned base and strides that are multiples of 4 floats";
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v)) return "q/k/v need 16-byte aligned base and strides";
   if (!(p.scale > 0.f)) return "sm_scale must be positive";
   if (p.final_out.ptr && !aligned16(p.final_out)) return "out needs a 16-byte aligned base and strides";

@@ -249,6 +249,57 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// ---- packed fp32 pairs and other arithmetic helpers of the softmax loops ---------------------
+// Two floats in one 64-bit register pair: fma / add on both halves in one instruction.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x for a pair of exponents on the FMA pipe instead of the special-function unit, which is
+// the busiest unit of the forward kernel: x = n + f with n = round(x) taken from the low
+// mantissa bits of x + 1.5 * 2^23, 2^f on [-0.5, 0.5] by a cubic with unit constant term
+// (largest relative error 1.0e-4, well under the 2^-9 rounding of the bf16 result it feeds),
+// n added to the exponent field.  x below -127 (a masked pair: -inf) gives exactly 0, like
+// ex2.approx.ftz; x must stay below 128.  A NaN exponent gives a finite value here, so a row
+// only keeps the NaN of a non-finite input score through its special-function columns.
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& r0, float& r1) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x2 = pack2(fmaxf(x0, -127.f), fmaxf(x1, -127.f));
+  const uint64_t magic = pack2(12582912.f, 12582912.f), neg_magic = pack2(-12582912.f, -12582912.f);
+  const uint64_t t2 = add2(x2, magic);
+  const uint64_t n2 = add2(t2, neg_magic);
+  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), x2);
+  uint64_t p2 = fma2(f2, pack2(0.05500893294811249f, 0.05500893294811249f), pack2(0.24221095442771912f, 0.24221095442771912f));
+  p2 = fma2(p2, f2, pack2(0.6932829022407532f, 0.6932829022407532f));
+  p2 = fma2(p2, f2, pack2(1.f, 1.f));
+  float p0, p1, t0, t1;
+  unpack2(p2, p0, p1);
+  unpack2(t2, t0, t1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

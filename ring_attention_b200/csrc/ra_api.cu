@@ -210,7 +210,7 @@ int ra_fwd_finalize(const ra_shape_t* shape, const float* o, const float* m, con
   if ((rc = check_shape(shape))) return rc;
   if ((rc = check_tensor(out, "out"))) return rc;
   if (!o || !m || !l) return fail(-6, "carried state (o, m, l) is NULL");
-  cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, o, m, l, view(out),
+  cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, o, m, l, nullptr, nullptr, nullptr, view(out),
                                   shape->dtype, lse, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail_cuda(e, "finalize");
   return 0;

@@ -19,8 +19,10 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -143,11 +145,17 @@ namespace ringimpl {
 // Flag page of one rank (64-bit counters, all monotonic over the life of the ring).
 //   KV_READY[slot]   written by the rank that pushed a K/V block into stage[slot]: global step id
 //   PART_READY[slot] written by the rank that pushed a dK/dV contribution into rpart[slot]
-//   PROGRESS[j]      written by rank j: number of block steps j has finished (frees stage slots)
+//   PROGRESS[lane][j] written by rank j: global id up to which j has finished the block steps of
+//                    one compute lane (frees that lane's stage slot)
 //   ADDED[j]         written by rank j: global id up to which j has summed received contributions
+// Block steps alternate between two compute lanes (even steps on the caller's stream, odd steps
+// on a second compute stream of the ring), so that the tail of one block kernel overlaps the
+// head of the next; a step's staging slot, contribution buffer, forward state and PROGRESS
+// counter are those of its lane (slot = lane = step parity), and steps of one lane stay ordered.
 constexpr int kMaxRanks = 64;
-constexpr int kFlagKvReady = 0, kFlagPartReady = 2, kFlagProgress = 8, kFlagAdded = 8 + kMaxRanks;
-constexpr int kNumFlags = 8 + 2 * kMaxRanks;
+constexpr int kFlagKvReady = 0, kFlagPartReady = 2, kFlagProgress = 8, kFlagAdded = 8 + 2 * kMaxRanks;
+constexpr int kNumFlags = 8 + 3 * kMaxRanks;
+constexpr int progress_flag(int lane, int rank) { return kFlagProgress + lane * kMaxRanks + rank; }
 constexpr uint32_t kStRingWait = 1u << 16;  // status bit: a cross-GPU wait ran out
 
 struct FlagList {
@@ -209,6 +217,8 @@ struct ra_ring {
   ncclComm_t comm = nullptr;
   cudaStream_t push_stream = nullptr;    // transfers this rank issues (high priority)
   cudaStream_t reduce_stream = nullptr;  // sums of dK/dV contributions this rank receives (p2p)
+  cudaStream_t lane_stream = nullptr;    // second compute lane: the odd block steps
+  cudaEvent_t ev_lane_start = nullptr, ev_lane_done = nullptr;
   cudaEvent_t ev_start = nullptr, ev_recv[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
   cudaEvent_t ev_part[2] = {nullptr, nullptr}, ev_sent[2] = {nullptr, nullptr}, ev_tail = nullptr;
   cudaEvent_t ev_push_tail = nullptr, ev_step0 = nullptr;
@@ -616,7 +626,7 @@ int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
     // the consumer's stage[slot] was last read by its step t-2 (or by its previous call)
     const uint64_t need = t >= 3 ? r->epoch + t - 1 : r->epoch;
     int rc;
-    if ((rc = launch_wait(r, r->push_stream, kFlagProgress + to, need))) return rc;
+    if ((rc = launch_wait(r, r->push_stream, progress_flag(slot, to), need))) return rc;
     double sent = 0;
     for (int i = 0; i < msg.n; ++i) sent += (double)msg.bytes[i];
     if ((rc = push_mark(r, r->push_stream, sent))) return rc;
@@ -645,7 +655,7 @@ int wait_kv(ra_ring_t* r, int t, cudaStream_t stream) {
 // After the block kernel of step t: tell the ranks that may want to overwrite the slot.
 int step_done(ra_ring_t* r, int t, cudaStream_t stream) {
   if (r->nranks == 1) return 0;
-  if (r->p2p) return launch_set(r, stream, -1, kFlagProgress + r->rank, r->epoch + t + 1);
+  if (r->p2p) return launch_set(r, stream, -1, progress_flag(t & 1, r->rank), r->epoch + t + 1);
   RA_CUDA(cudaEventRecord(r->ev_done[t & 1], stream), "cudaEventRecord");
   return 0;
 }
@@ -656,6 +666,7 @@ int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
     RA_CUDA(cudaEventRecord(ring->ev_start, stream), "cudaEventRecord");
     RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
     if (ring->reduce_stream) RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
+    RA_CUDA(cudaStreamWaitEvent(ring->lane_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
   }
   ring->dir = dir;
   ring->t_used[dir] = 0;
@@ -666,8 +677,22 @@ int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
   return 0;
 }
 
+// The second lane's work of this call is over: move its PROGRESS counter to the call's end and
+// make the caller's stream wait for it.
+int join_lane(ra_ring_t* ring, cudaStream_t stream) {
+  if (ring->nranks == 1) return 0;
+  int rc;
+  if (ring->p2p && (rc = launch_set(ring, ring->lane_stream, -1, progress_flag(1, ring->rank), ring->epoch + ring->nranks))) return rc;
+  RA_CUDA(cudaEventRecord(ring->ev_lane_done, ring->lane_stream), "cudaEventRecord");
+  RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_lane_done, 0), "cudaStreamWaitEvent");
+  return 0;
+}
+
 int end_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
   if (ring->nranks > 1) {
+    // both lanes' counters end the call at epoch + nranks: the next call's first pushes wait for that
+    int rc;
+    if (ring->p2p && (rc = launch_set(ring, stream, -1, progress_flag(0, ring->rank), ring->epoch + ring->nranks))) return rc;
     // the pushes read the caller's tensors: they must be over before the caller may reuse them
     RA_CUDA(cudaEventRecord(ring->ev_push_tail, ring->push_stream), "cudaEventRecord");
     RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_push_tail, 0), "cudaStreamWaitEvent");
@@ -735,11 +760,12 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
   if ((e = cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaDeviceGetStreamPriorityRange"));
   if ((e = cudaStreamCreateWithPriority(&r->push_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
-      (e = cudaStreamCreateWithPriority(&r->reduce_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess)
+      (e = cudaStreamCreateWithPriority(&r->reduce_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
+      (e = cudaStreamCreateWithPriority(&r->lane_stream, cudaStreamNonBlocking, prio_low)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaStreamCreate"));
   cudaEvent_t* evs[] = {&r->ev_start, &r->ev_recv[0], &r->ev_recv[1], &r->ev_done[0], &r->ev_done[1],
                         &r->ev_part[0], &r->ev_part[1], &r->ev_sent[0], &r->ev_sent[1], &r->ev_tail,
-                        &r->ev_push_tail, &r->ev_step0};
+                        &r->ev_push_tail, &r->ev_step0, &r->ev_lane_start, &r->ev_lane_done};
   for (cudaEvent_t* ev : evs)
     if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess)
       return bail(fail_cuda(e, "cudaEventCreate"));
@@ -779,6 +805,7 @@ int ra_ring_destroy(ra_ring_t* r) {
   if (!r) return 0;
   if (r->push_stream) cudaStreamSynchronize(r->push_stream);
   if (r->reduce_stream) cudaStreamSynchronize(r->reduce_stream);
+  if (r->lane_stream) cudaStreamSynchronize(r->lane_stream);
   if (r->p2p) close_peers(r);
   if (r->comm) {
     NcclApi* api = nccl_api();
@@ -786,7 +813,8 @@ int ra_ring_destroy(ra_ring_t* r) {
   }
   cudaEvent_t evs[] = {r->ev_start, r->ev_recv[0], r->ev_recv[1], r->ev_done[0], r->ev_done[1],
                        r->ev_part[0], r->ev_part[1], r->ev_sent[0], r->ev_sent[1], r->ev_tail,
-                       r->ev_push_tail, r->ev_step0, r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
+                       r->ev_push_tail, r->ev_step0, r->ev_lane_start, r->ev_lane_done, r->t_begin[0], r->t_begin[1],
+                       r->t_end[0], r->t_end[1]};
   for (cudaEvent_t ev : evs)
     if (ev) cudaEventDestroy(ev);
   for (int d = 0; d < 2; ++d) {
@@ -796,6 +824,7 @@ int ra_ring_destroy(ra_ring_t* r) {
   }
   if (r->push_stream) cudaStreamDestroy(r->push_stream);
   if (r->reduce_stream) cudaStreamDestroy(r->reduce_stream);
+  if (r->lane_stream) cudaStreamDestroy(r->lane_stream);
   r->state.release();
   r->grads.release();
   for (int i = 0; i < 2; ++i) {
@@ -851,6 +880,37 @@ int ra_ring_transport(const ra_ring_t* r) {
   return r->nranks == 1 ? 0 : (r->p2p ? 1 : 2);
 }
 
+namespace ringimpl {
+// [begin, end) offsets in ms from the call's first event, one interval per pair of events.
+int event_intervals(cudaEvent_t origin, const std::vector<cudaEvent_t>& ev, size_t used,
+                    std::vector<std::pair<float, float>>* out) {
+  out->clear();
+  for (size_t i = 0; i + 1 < used; i += 2) {
+    float a = 0.f, b = 0.f;
+    RA_CUDA(cudaEventElapsedTime(&a, origin, ev[i]), "cudaEventElapsedTime");
+    RA_CUDA(cudaEventElapsedTime(&b, origin, ev[i + 1]), "cudaEventElapsedTime");
+    out->push_back({a, b > a ? b : a});
+  }
+  return 0;
+}
+
+// Sorted, disjoint union of intervals.
+std::vector<std::pair<float, float>> interval_union(std::vector<std::pair<float, float>> v) {
+  std::sort(v.begin(), v.end());
+  std::vector<std::pair<float, float>> u;
+  for (const auto& iv : v) {
+    if (!u.empty() && iv.first <= u.back().second)
+      u.back().second = std::max(u.back().second, iv.second);
+    else
+      u.push_back(iv);
+  }
+  return u;
+}
+}  // namespace ringimpl
+
+// Exposed wait = the part of each wait for a transfer during which no block kernel of this
+// rank was running (with two compute lanes a wait on one lane is hidden while the other lane
+// computes).
 int ra_ring_last_timing(ra_ring_t* r, int32_t backward, float* total_ms, float* exposed_ms) {
   if (!r) return fail(-30, "ring handle is NULL");
   if (!r->timing) return fail(-35, "timing is off: call ra_ring_set_timing(ring, 1) first");
@@ -858,10 +918,18 @@ int ra_ring_last_timing(ra_ring_t* r, int32_t backward, float* total_ms, float* 
   RA_CUDA(cudaEventSynchronize(r->t_end[d]), "cudaEventSynchronize");
   float tot = 0.f, exp = 0.f;
   RA_CUDA(cudaEventElapsedTime(&tot, r->t_begin[d], r->t_end[d]), "cudaEventElapsedTime");
-  for (size_t i = 0; i + 1 < r->t_used[d]; i += 2) {
-    float ms = 0.f;
-    RA_CUDA(cudaEventElapsedTime(&ms, r->t_events[d][i], r->t_events[d][i + 1]), "cudaEventElapsedTime");
-    exp += ms;
+  std::vector<std::pair<float, float>> waits, blocks;
+  int rc;
+  if ((rc = event_intervals(r->t_begin[d], r->t_events[d], r->t_used[d], &waits))) return rc;
+  if ((rc = event_intervals(r->t_begin[d], r->b_events[d], r->b_used[d], &blocks))) return rc;
+  const auto busy = interval_union(blocks);
+  for (const auto& w : waits) {
+    float hidden = 0.f;
+    for (const auto& k : busy) {
+      const float lo = std::max(w.first, k.first), hi = std::min(w.second, k.second);
+      if (hi > lo) hidden += hi - lo;
+    }
+    exp += (w.second - w.first) - hidden;
   }
   if (total_ms) *total_ms = tot;
   if (exposed_ms) *exposed_ms = exp;
@@ -891,12 +959,12 @@ int ra_ring_last_block_ms(ra_ring_t* r, int32_t backward, float* block_ms, int32
   const int dir = backward ? 1 : 0;
   if (r->b_used[dir] == 0) return fail(-38, "no %s call has been timed yet", dir ? "backward" : "forward");
   RA_CUDA(cudaEventSynchronize(r->t_end[dir]), "cudaEventSynchronize");
+  // device time during which at least one block kernel ran (kernels of the two lanes overlap)
+  std::vector<std::pair<float, float>> blocks;
+  int rc;
+  if ((rc = event_intervals(r->t_begin[dir], r->b_events[dir], r->b_used[dir], &blocks))) return rc;
   float sum = 0.f;
-  for (size_t i = 0; i + 1 < r->b_used[dir]; i += 2) {
-    float ms = 0.f;
-    RA_CUDA(cudaEventElapsedTime(&ms, r->b_events[dir][i], r->b_events[dir][i + 1]), "cudaEventElapsedTime");
-    sum += ms;
-  }
+  for (const auto& k : interval_union(blocks)) sum += k.second - k.first;
   if (block_ms) *block_ms = sum;
   if (launches) *launches = (int32_t)(r->b_used[dir] / 2);
   return 0;
@@ -930,11 +998,20 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   p.scale = shape->sm_scale;
 
   const RingSizes z = ring_sizes(shape, N);
-  const size_t o_bytes = z.o_bytes, ml_bytes = z.ml_bytes;
-  RA_CUDA(ring->state.reserve(o_bytes + 2 * ml_bytes), "cudaMalloc(state)");
-  p.o = (float*)ring->state.ptr;
-  p.m = (float*)((char*)ring->state.ptr + o_bytes);
-  p.l = (float*)((char*)ring->state.ptr + o_bytes + ml_bytes);
+  const size_t o_bytes = z.o_bytes, ml_bytes = z.ml_bytes, state_bytes = o_bytes + 2 * ml_bytes;
+  // one carried state (o, m, l) per compute lane: even steps fold into the first, odd steps into
+  // the second, and the two are merged at the end (the online-softmax update of ring.py:58-76 is
+  // associative), so that adjacent steps do not depend on each other
+  const int n_lanes = N > 1 ? 2 : 1;
+  RA_CUDA(ring->state.reserve(n_lanes * state_bytes), "cudaMalloc(state)");
+  float *st_o[2], *st_m[2], *st_l[2];
+  for (int ln = 0; ln < 2; ++ln) {
+    char* base = (char*)ring->state.ptr + (ln < n_lanes ? ln : 0) * state_bytes;
+    st_o[ln] = (float*)base;
+    st_m[ln] = (float*)(base + o_bytes);
+    st_l[ln] = (float*)(base + o_bytes + ml_bytes);
+  }
+  cudaStream_t lane_s[2] = {stream, N > 1 ? ring->lane_stream : stream};
 
   ring->ignore_plan = (p.mod.kinds & RA_MOD_STRICT_NAN) != 0;
   KvMessage msg = make_kv_message(shape, p.k, p.v, p.mod);
@@ -947,35 +1024,40 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   if (ring->plan && ring->plan->nranks != N) return fail(-39, "the plan was made for a ring of %d ranks", ring->plan->nranks);
   const int me_f = ring->rank;
   auto source = [&](int t) { return ((me_f - t) % N + N) % N; };
-  int t_last = 0;  // last step that runs (the own block always does)
-  for (int t = 1; t < N; ++t)
-    if (pair_needed(ring, me_f, source(t))) t_last = t;
+  bool used[2] = {false, false};
   for (int t = 0; t < N; ++t) {
+    const int ln = t & (n_lanes - 1);
+    cudaStream_t s = lane_s[ln];
     if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;  // runs under step t
     if (t > 0 && !pair_needed(ring, me_f, source(t))) {  // nothing visible in this block: no wait, no launch
-      if ((rc = step_done(ring, t, stream))) return rc;
+      if ((rc = step_done(ring, t, s))) return rc;
       continue;
     }
     p.k = k_own;
     p.v = v_own;
     p.mod = mod_own;
+    p.o = st_o[ln];
+    p.m = st_m[ln];
+    p.l = st_l[ln];
     if (t > 0) {
       use_staged(msg, ring->stage[t & 1], &p.k, &p.v, &p.mod);
-      if ((rc = wait_kv(ring, t, stream))) return rc;
+      if ((rc = wait_kv(ring, t, s))) return rc;
     }
-    p.first = (t == 0);
-    if (t == t_last) {  // the tensor-core kernel normalises and writes out / L itself on the last block
+    p.first = !used[ln];
+    used[ln] = true;
+    if (N == 1) {  // ring of one: the tensor-core kernel normalises and writes out / L itself
       p.final_out = out_view;
       p.final_lse = lse;
     }
-    if ((rc = block_mark(ring, 0, stream))) return rc;
-    if ((rc = run_fwd_block(p, shape->dtype, stream))) return rc;
-    if ((rc = block_mark(ring, 0, stream))) return rc;
-    if ((rc = step_done(ring, t, stream))) return rc;
+    if ((rc = block_mark(ring, 0, s))) return rc;
+    if ((rc = run_fwd_block(p, shape->dtype, s))) return rc;
+    if ((rc = block_mark(ring, 0, s))) return rc;
+    if ((rc = step_done(ring, t, s))) return rc;
   }
-  if (last_impl() != RA_IMPL_TCGEN05) {  // the CUDA-core kernel stored the carried state: ring.py:134-135 here
-    cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, p.o, p.m, p.l, out_view,
-                                    shape->dtype, lse, stream);
+  if ((rc = join_lane(ring, stream))) return rc;
+  if (N > 1 || last_impl() != RA_IMPL_TCGEN05) {  // ring.py:134-135 over the merged states of the lanes
+    cudaError_t e = launch_finalize(shape->b, shape->h, shape->lq, shape->dv, st_o[0], st_m[0], st_l[0],
+                                    used[1] ? st_o[1] : nullptr, st_m[1], st_l[1], out_view, shape->dtype, lse, stream);
     if (e != cudaSuccess) return fail_cuda(e, "finalize");
   }
   // no contributions were exchanged in this call: move this rank's ADDED counter to the call's end
@@ -1111,9 +1193,18 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
 
   NcclApi* api = N > 1 ? nccl_api() : nullptr;
   cudaStream_t add_stream = ring->p2p ? ring->reduce_stream : ring->push_stream;
+  // even steps on the caller's stream, odd steps on the second compute lane: adjacent block
+  // kernels share nothing but the dQ accumulator (added to with reductions), so the tail of one
+  // overlaps the head of the next
+  cudaStream_t lane_s[2] = {stream, N > 1 ? ring->lane_stream : stream};
+  if (N > 1) {  // delta is computed and the accumulators are cleared
+    RA_CUDA(cudaEventRecord(ring->ev_lane_start, stream), "cudaEventRecord");
+    RA_CUDA(cudaStreamWaitEvent(ring->lane_stream, ring->ev_lane_start, 0), "cudaStreamWaitEvent");
+  }
   const TensorView k_own = p.k, v_own = p.v;
   const ModParams mod_own = p.mod;
   for (int t = 0; t < N; ++t) {
+    cudaStream_t s = lane_s[t & 1];
     if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;
     p.k = k_own;
     p.v = v_own;
@@ -1122,12 +1213,12 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       p.dk = dk_acc;
       p.dv = dv_acc;
       const BwdParams first = split ? sub_problem(p, esize, 0, split_b ? b0 : shape->b, 0, split_h ? h0 : shape->h) : p;
-      if ((rc = block_mark(ring, 1, stream))) return rc;
-      if ((rc = run_bwd_block(first, shape->dtype, stream))) return rc;
-      if ((rc = block_mark(ring, 1, stream))) return rc;
-      if ((rc = step_done(ring, 0, stream))) return rc;
+      if ((rc = block_mark(ring, 1, s))) return rc;
+      if ((rc = run_bwd_block(first, shape->dtype, s))) return rc;
+      if ((rc = block_mark(ring, 1, s))) return rc;
+      if ((rc = step_done(ring, 0, s))) return rc;
       if (N > 1) {  // the sums of received contributions start after the accumulators were cleared and the own block's part added
-        RA_CUDA(cudaEventRecord(ring->ev_step0, stream), "cudaEventRecord");
+        RA_CUDA(cudaEventRecord(ring->ev_step0, s), "cudaEventRecord");
         if (ring->p2p) RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_step0, 0), "cudaStreamWaitEvent");
       }
       continue;
@@ -1139,21 +1230,21 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     const bool compute = pair_needed(ring, me, owner), receive = pair_needed(ring, giver, me);
     if (compute) {
       use_staged(msg, ring->stage[slot], &p.k, &p.v, &p.mod);
-      if ((rc = wait_kv(ring, t, stream))) return rc;
-      // this step's contribution to the remote block's dK/dV, built from zero
-      if (t >= 3) RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
+      if ((rc = wait_kv(ring, t, s))) return rc;
+      // part[slot] was last sent two steps ago, by this lane
+      if (t >= 3) RA_CUDA(cudaStreamWaitEvent(s, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
       // this step's contribution is built from nothing: the kernel stores instead of adding
       p.dk = (float*)ring->part[slot].ptr;
       p.dv = (float*)((char*)ring->part[slot].ptr + dk_b);
       p.overwrite = 1;
-      if ((rc = block_mark(ring, 1, stream))) return rc;
-      if ((rc = run_bwd_block(p, shape->dtype, stream))) return rc;
-      if ((rc = block_mark(ring, 1, stream))) return rc;
+      if ((rc = block_mark(ring, 1, s))) return rc;
+      if ((rc = run_bwd_block(p, shape->dtype, s))) return rc;
+      if ((rc = block_mark(ring, 1, s))) return rc;
       p.overwrite = 0;
     }
-    if ((rc = step_done(ring, t, stream))) return rc;
+    if ((rc = step_done(ring, t, s))) return rc;
     if (compute) {
-      RA_CUDA(cudaEventRecord(ring->ev_part[slot], stream), "cudaEventRecord");
+      RA_CUDA(cudaEventRecord(ring->ev_part[slot], s), "cudaEventRecord");
       // give it to the block's owner; take what another rank computed for this rank's block
       RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
     }
@@ -1189,6 +1280,10 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   }
   if (N > 1) RA_CUDA(cudaEventRecord(ring->ev_tail, add_stream), "cudaEventRecord");
   if (split) {
+    // on the lane of the last remote step, behind it: that step's contribution then travels and
+    // is summed while this part runs (on the other lane the two kernels would share the GPU and
+    // end together, with the transfer exposed after them)
+    cudaStream_t s = lane_s[(N - 1) & 1];
     p.k = k_own;
     p.v = v_own;
     p.mod = mod_own;
@@ -1198,10 +1293,11 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     second.dk = own2_dk;
     second.dv = own2_dv;
     second.overwrite = 1;  // built from nothing: no clearing pass
-    if ((rc = block_mark(ring, 1, stream))) return rc;
-    if ((rc = run_bwd_block(second, shape->dtype, stream))) return rc;
-    if ((rc = block_mark(ring, 1, stream))) return rc;
+    if ((rc = block_mark(ring, 1, s))) return rc;
+    if ((rc = run_bwd_block(second, shape->dtype, s))) return rc;
+    if ((rc = block_mark(ring, 1, s))) return rc;
   }
+  if ((rc = join_lane(ring, stream))) return rc;
   if (N > 1 && (rc = wait_transfer(ring, stream, ring->ev_tail))) return rc;
   if (split) {
     const int64_t off = ((int64_t)b0 * shape->h + h0) * shape->lk;

@@ -427,11 +427,14 @@ __device__ __forceinline__ void store_from_float<__nv_bfloat16>(__nv_bfloat16* p
   *p = __float2bfloat16_rn(x);
 }
 
-// out = o / l ; L = m + log l (ring.py:134-135).  One warp per row.
+// out = o / l ; L = m + log l (ring.py:134-135).  One warp per row.  With a second state
+// (o2, m2, l2) the two are merged first: m = max(m, m2), each side scaled by exp(m_side - m)
+// (0 for a side that saw nothing), exactly the update of ring.py:63-75.
 template <typename T>
 __global__ void finalize_kernel(int b, int h, int lq, int dv, const float* __restrict__ o,
                                 const float* __restrict__ m, const float* __restrict__ l,
-                                TensorView out, float* __restrict__ lse) {
+                                const float* __restrict__ o2, const float* __restrict__ m2,
+                                const float* __restrict__ l2, TensorView out, float* __restrict__ lse) {
   int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   int lane = threadIdx.x & 31;
   int64_t nrows = (int64_t)b * h * lq;
@@ -439,10 +442,21 @@ __global__ void finalize_kernel(int b, int h, int lq, int dv, const float* __res
   int r = (int)(row % lq);
   int hh = (int)((row / lq) % h);
   int bb = (int)(row / ((int64_t)lq * h));
-  float lv = l[row], mv = m[row];
+  float lv = l[row], mv = m[row], c1 = 1.f, c2 = 0.f;
+  if (o2) {
+    const float ma = mv, mb = m2[row];
+    mv = fmaxf(ma, mb);
+    c1 = (ma == -INFINITY) ? 0.f : expf(ma - mv);
+    c2 = (mb == -INFINITY) ? 0.f : expf(mb - mv);
+    lv = lv * c1 + l2[row] * c2;
+  }
   if (lane == 0 && lse) lse[row] = mv + logf(lv);
   T* dst = (T*)out.ptr + (int64_t)bb * out.sb + (int64_t)r * out.sl + (int64_t)hh * out.sh;
-  for (int c = lane; c < dv; c += 32) store_from_float(dst + c, o[row * dv + c] / lv);
+  for (int c = lane; c < dv; c += 32) {
+    float v = o[row * dv + c] * c1;
+    if (o2) v += o2[row * dv + c] * c2;
+    store_from_float(dst + c, v / lv);
+  }
 }
 
 // delta = rowsum(out * dout) (ring_kernel.py:387-409; ring.py:151).  One warp per row.
@@ -564,14 +578,15 @@ cudaError_t simt_bwd_block(const BwdParams& p, int dtype, cudaStream_t s) {
   return dtype == RA_DTYPE_F32 ? dispatch_bwd<float>(p, s) : dispatch_bwd<__nv_bfloat16>(p, s);
 }
 
-cudaError_t launch_finalize(int b, int h, int lq, int dv, const float* o, const float* m,
-                            const float* l, TensorView out, int dtype, float* lse, cudaStream_t s) {
+cudaError_t launch_finalize(int b, int h, int lq, int dv, const float* o, const float* m, const float* l,
+                            const float* o2, const float* m2, const float* l2, TensorView out, int dtype,
+                            float* lse, cudaStream_t s) {
   int64_t rows = (int64_t)b * h * lq;
   int grid = (int)((rows + 7) / 8);
   if (dtype == RA_DTYPE_F32)
-    finalize_kernel<float><<<grid, 256, 0, s>>>(b, h, lq, dv, o, m, l, out, lse);
+    finalize_kernel<float><<<grid, 256, 0, s>>>(b, h, lq, dv, o, m, l, o2, m2, l2, out, lse);
   else
-    finalize_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(b, h, lq, dv, o, m, l, out, lse);
+    finalize_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(b, h, lq, dv, o, m, l, o2, m2, l2, out, lse);
   count_launch();
   return cudaGetLastError();
 }

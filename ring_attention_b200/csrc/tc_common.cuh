@@ -57,11 +57,18 @@ constexpr uint32_t kMetaKinds = kMaskKinds | RA_MOD_ALIBI;
 // contiguous (`col_contig`: position of column c is col_pos0 + c) they are not loaded.
 // kRowIsQuery: the thread's row is a query and columns are keys (forward); else the thread's
 // row is a key and columns are queries (backward, transposed tiles).
+// A dense bias tile (RA_MOD_DENSE: the materialised bias_fn result of ring.py:60-61) is added
+// here as well, divided by the scale like the ALiBi term: `bias` points at this thread's row
+// and the tile's first column, consecutive columns are `bias_col_stride` floats apart (1 in the
+// forward, where a thread reads 64 contiguous bytes per 16 columns; the bias row stride in the
+// backward, where the lanes of a warp read consecutive floats of one bias row).
 template <bool kRowIsQuery>
 __device__ __noinline__ void fixup_scores_tmem(uint32_t taddr, int ncols, uint32_t kinds, int32_t window,
                                                float alibi_over_scale, int32_t row_pos, int32_t row_seg,
                                                bool row_pre, const int32_t* col_pos, const int32_t* col_seg,
-                                               const uint8_t* col_pre, int32_t col_pos0, bool col_contig) {
+                                               const uint8_t* col_pre, int32_t col_pos0, bool col_contig,
+                                               const float* bias = nullptr, int64_t bias_col_stride = 1,
+                                               float inv_scale = 0.f) {
   uint32_t cur[16], nxt[16];
   ptx::tmem_ld16(taddr, cur);
 #pragma unroll 1
@@ -69,6 +76,21 @@ __device__ __noinline__ void fixup_scores_tmem(uint32_t taddr, int ncols, uint32
     ptx::tc_wait_ld();
     const bool more = c0 + 16 < ncols;
     if (more) ptx::tmem_ld16(taddr + c0 + 16, nxt);
+    if (bias) {
+      float bv[16];
+      if constexpr (kRowIsQuery) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + c0) + j);
+          bv[4 * j] = b4.x, bv[4 * j + 1] = b4.y, bv[4 * j + 2] = b4.z, bv[4 * j + 3] = b4.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) bv[e] = __ldg(bias + (int64_t)(c0 + e) * bias_col_stride);
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) cur[e] = __float_as_uint(fmaf(bv[e], inv_scale, __uint_as_float(cur[e])));
+    }
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
       const int32_t cpos = col_contig ? col_pos0 + c0 + e : (col_pos ? __ldg(col_pos + c0 + e) : 0);

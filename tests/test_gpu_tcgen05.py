@@ -173,3 +173,40 @@ def test_emulated_ring_of_eight_causal_with_state():
     out = (o / l[..., None]).permute(0, 2, 1, 3)
     check_close(out, ref[:, sl], BF, "out")
     check_close(m + torch.log(l), ref_lse[:, :, sl], torch.float32, "lse", 2e-3)
+
+
+@pytest.mark.parametrize("seed,lq,lk,h,d,head_bias", [(3, 1024, 1024, 2, 128, True), (5, 640, 896, 3, 64, False),
+                                                       (6, 256, 384, 2, 128, True)])
+def test_bias_fn_callable_runs_on_the_tensor_core_kernels(seed, lq, lk, h, d, head_bias):
+    """ring_test.py:174-300 on the tcgen05 path: any callable's dense bias tile (ring.py:107) is
+    added inside the tensor-core kernels; rows that see no key are NaN exactly where dense
+    softmax is (ring_test.py:273), and so are the gradients they poison (ring.py:146)."""
+    from ring_attention_b200._lib import RA_IMPL_TCGEN05, lib
+
+    q, k, v, do, rng = make_inputs(seed, 2, lq, lk, h, d, BF)
+    qseg = rng.integers(0, max(lq // 5, 1), (2, lq)).astype(np.int32)
+    kseg = rng.integers(0, max(lq // 5, 1), (2, lk)).astype(np.int32)
+    qseg[:, 5] = 10 ** 6  # a query row that no key shares a segment with
+    extra = rng.standard_normal((2, h if head_bias else 1, lq, lk)) * 0.5  # a real additive term, not only a mask
+    bias = np.where((qseg[:, :, None] == kseg[:, None, :])[:, None], extra, -np.inf)
+    bias = np.broadcast_to(bias, (2, h, lq, lk))
+    tex = to_dev(extra, torch.float32)
+
+    def bias_fn(q_segment_ids, kv_segment_ids):
+        mask = (q_segment_ids[:, :, None] == kv_segment_ids[:, None, :])[:, None]
+        return torch.where(mask, tex, torch.full_like(tex, float("-inf")))  # [b, h or 1, lq, lk]
+
+    tq, tk, tv, tdo = (to_dev(x, BF) for x in (q, k, v, do))
+    kw = dict(bias_q_kwargs={"q_segment_ids": to_dev(qseg, torch.int32)},
+              bias_kv_kwargs={"kv_segment_ids": to_dev(kseg, torch.int32)})
+    out, dq, dk, dv = _grads(lambda a, b, c: ra().ring_attention(a, b, c, "sp", bias_fn=bias_fn, block_impl="tcgen05", **kw),
+                             tq, tk, tv, tdo)
+    assert lib.ra_last_impl() == RA_IMPL_TCGEN05
+    _status_clean()
+    ref = O.mha(q, k, v, bias)
+    rq, rk, rv = O.mha_grads(q, k, v, do, bias)
+    assert np.isnan(ref).any(), "the case should have rows that see no key"
+    check_close(out, ref, BF, "out")
+    check_close(dq, rq, BF, "dq")
+    check_close(dk, rk, BF, "dk")
+    check_close(dv, rv, BF, "dv")
