@@ -568,6 +568,41 @@ def main():
                     ev_out.record(s_out)
             main.wait_event(ev_out)
 
+        # What the host side can deliver: one pinned tensor copied in and one copied out, first by
+        # one rank at a time (the others idle), then by all ranks at once.  The second figure is the
+        # ceiling of the end-to-end number when the step itself gets short.
+        def copy_rate(active):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            a0.record()
+            if active:
+                for _ in range(3):
+                    dev_in[0][0].copy_(host_in[0], non_blocking=True)
+                    host_out[0].copy_(dev_in[1][0], non_blocking=True)
+            a1.record()
+            barrier()
+            ms = a0.elapsed_time(a1) / 3
+            return (2 * host_in[0].numel() * host_in[0].element_size() / (ms * 1e-3) / 1e9) if active and ms > 0 else 0.0
+
+        copy_rate(True)  # touch the buffers once
+        alone = 0.0
+        for turn in range(world):
+            r_ = copy_rate(turn == rank)
+            alone = r_ if turn == rank else alone
+        together = copy_rate(True)
+        rates_t = torch.tensor([alone, together], device="cuda")
+        if world > 1:
+            gathered_r = [torch.zeros_like(rates_t) for _ in range(world)]
+            dist.all_gather(gathered_r, rates_t)
+            rates_all = torch.stack(gathered_r).cpu()
+        else:
+            rates_all = rates_t.cpu()[None]
+        host_probe = {"gb_per_s_one_rank_alone_mean": float(rates_all[:, 0].mean()),
+                      "gb_per_s_per_rank_all_copying_mean": float(rates_all[:, 1].mean()),
+                      "gb_per_s_all_ranks_together": float(rates_all[:, 1].sum()),
+                      "note": "one pinned tensor copied in, then one copied out, per rank (one direction at a time): "
+                              "bytes moved / device time"}
+
         e2e_run(min(args.warmup, 2))
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -615,7 +650,7 @@ def main():
                "copies": "own streams, double-buffered on the device, inside the timed region",
                "inline_ms_per_step": float(ti.item()),
                "host_gb_per_s_each_way_all_ranks": world * h2d / (float(t.item()) * 1e-3) / 1e9,
-               "matches_device_resident_results": bool(same), "host": host_info}
+               "matches_device_resident_results": bool(same), "host": host_info, "host_copy_probe": host_probe}
 
     if rank == 0:
         pk = peaks()

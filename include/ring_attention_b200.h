@@ -270,6 +270,15 @@ int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score
                         ra_ring_plan_t** plan);
 void ra_ring_plan_destroy(ra_ring_plan_t* plan);
 int ra_ring_plan_need(const ra_ring_plan_t* plan, int32_t q_rank, int32_t kv_rank);
+/* The plan also bounds WHICH rows of a needed block matter: up to two runs of K/V rows (one in
+ * each half of the block, in 128-row units) outside which the queries of q_rank see nothing.
+ * Under a plan only those rows of K and V travel (the small per-token arrays always travel
+ * whole) and only those rows of the dK/dV contribution come back and are summed: a sliding
+ * window or a document boundary inside a block moves a halo, not the block (the reference
+ * rotates whole blocks, ring.py:120, :195).  runs = {first0, end0, first1, end1} in rows;
+ * an empty run has first >= end.  Row runs need k and v laid out [b, l, h, d]; other dense
+ * layouts travel whole. */
+int ra_ring_plan_rows(const ra_ring_plan_t* plan, int32_t q_rank, int32_t kv_rank, int32_t runs[4]);
 int ra_ring_use_plan(ra_ring_t* ring, const ra_ring_plan_t* plan);
 
 /* Rotate caller-owned buffers one place round the ring (rank i -> rank i+1), the

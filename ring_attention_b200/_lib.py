@@ -74,6 +74,7 @@ _SIGNATURES = {
     "ra_ring_plan_create": (C.c_int, [C.c_void_p, _P(RaShape), _P(RaScoreMod), C.c_void_p, _P(C.c_void_p)]),
     "ra_ring_plan_destroy": (None, [C.c_void_p]),
     "ra_ring_plan_need": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
+    "ra_ring_plan_rows": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, _P(C.c_int32)]),
     "ra_ring_use_plan": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ra_ring_rotate": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_void_p), _P(C.c_void_p), _P(C.c_int64),
                                  C.c_void_p]),

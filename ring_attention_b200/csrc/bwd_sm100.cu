@@ -9,16 +9,19 @@
 // that owns TMEM lane r owns key row r:
 //   S^T  = K Q^T          (SS MMA, both operands K-major)            -> TMEM [0,128)
 //   dP^T = V dO^T         (SS MMA)                                   -> TMEM [128,256)
-//   P^T  = exp2(S^T * c - L)          written back over S^T as packed bf16 (TMEM)
-//   dS^T = P^T * (dP^T - delta)       written to shared memory as bf16 (128B swizzle)
+//   P^T  = exp2(S^T * c - L * log2 e)            written back over S^T as packed bf16 (TMEM)
+//   dS^T = P^T * (dP^T - delta) * scale          written to shared memory as bf16 (128B swizzle)
+//          (the per-row terms -L * log2 e and -delta * scale are computed once per backward, and
+//           the softmax scale rides on dS^T, so dQ and dK need no further scaling)
 //   dV  += P^T dO         (TS MMA: A from TMEM, B = dO read MN-major) -> TMEM [256,256+D)
 //   dK  += dS^T Q         (SS MMA: B = Q read MN-major)               -> TMEM [256+D,256+2D)
 //   dQ^T = K^T dS^T       (SS MMA: A = K read MN-major, B = dS^T tile read MN-major; head dim 128)
-//                          -> TMEM [128,256), over dP^T; lane = head-dim index.  Each compute warp
-//                             copies its 32 head-dim lanes x 16 queries at a time into a small
-//                             shared-memory buffer and hands it to the TMA unit, which adds it to
-//                             the fp32 accumulator (tiled bulk reduce-add): the SM's load/store
-//                             path, which the MMAs' operand reads share, sees plain stores only.
+//                          -> TMEM [128,256), over dP^T; lane = head-dim index.  Each compute
+//                             warpgroup copies 16 of its 64 queries x 128 head-dim lanes at a
+//                             time into a shared-memory buffer and hands it to the TMA unit,
+//                             which adds the 8 KB box to the fp32 accumulator (tiled bulk
+//                             reduce-add): the SM's load/store path, which the MMAs' operand
+//                             reads share, sees plain stores only.
 //                             (head dim 64 forms dQ = dS K instead and uses vector reductions.)
 // warps 0-7: compute (two warpgroups split the 128 query columns), warp 8: TMA producer,
 // warp 9: MMA issuer.
@@ -40,10 +43,16 @@ constexpr int kBwdThreads = 320;
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr unsigned kProducerPollNs = 100;
+// Of every 16 column pairs of P^T, how many get their exponentials from the polynomial on the
+// FMA pipe (the others use ex2 on the special-function unit).
+#ifndef RA_BWD_POLY_PAIRS
+#define RA_BWD_POLY_PAIRS 0
+#endif
+constexpr int kBwdPolyPairs = RA_BWD_POLY_PAIRS;
 
 struct BwdTcParams {
   CUtensorMap map_q, map_k, map_v, map_do;
-  CUtensorMap map_dq;  // fp32 [b*h*lq, 128], box {32, 16}: head dim 128 only
+  CUtensorMap map_dq;  // fp32 [b*h*lq, 128], box {128, 16}: head dim 128 only
   BwdParams p;
   const TileMeta* meta_q;
   const TileMeta* meta_kv;
@@ -77,7 +86,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   constexpr int DS_BYTES = kTileRows * kTileRows * 2;
   // Head dim 128 keeps one dO stage (a dO tile is free after dV of its query tile, three MMA
   // groups before the next tile's dP^T needs the next one) and spends the 32 KB on the dQ
-  // staging buffers: 8 compute warps x 2 buffers x [16 queries][32 head-dim lanes] fp32.
+  // staging buffers: 2 warpgroups x 2 buffers x [16 queries][128 head-dim lanes] fp32.
   constexpr int DO_ST = D == 128 ? 1 : 2;
   constexpr int DQ_STAGE_BYTES = D == 128 ? 8 * 2 * 16 * 32 * 4 : 0;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -134,25 +143,39 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   if (masked) mk = P.meta_kv[bb * P.n_kv_tiles + kt];
   // First query tile >= i that has a pair visible to this CTA's K/V tile (n_q_tiles if there is
   // none), with kMixedBit set when that tile mixes visible and masked pairs and kContigBit when
-  // its positions are contiguous.  All 32 lanes of a
-  // warp call it with the same i: each lane classifies one tile, so a long masked stretch (the
-  // tiles before the diagonal, other documents) costs one load latency per 32 tiles.
+  // its positions are contiguous.  All 32 lanes of a warp call it with the same i.  Each lane
+  // classifies one tile of a window of 32 consecutive tiles and the window stays in registers:
+  // the summaries are loaded once per 32 tiles, not once per tile (a load per tile put an L2
+  // round trip on the critical path of every role), and a long masked stretch (the tiles before
+  // the diagonal, other documents) costs one load per 32 tiles.
   constexpr int kMixedBit = 1 << 16, kContigBit = 1 << 17, kTileIdx = kMixedBit - 1;
-  auto next_active = [&](int i) -> int {
+  struct Window {
+    int base = -(1 << 30);  // first tile of the window
+    int cls = 0;            // this lane's tile: 0 skip, 1 all visible, 2 mixed; +4 contiguous positions
+    int32_t pos0 = 0;       // first position of this lane's tile (valid when contiguous)
+    int32_t hit_pos0 = 0;   // pos0 of the tile the last call returned
+  };
+  auto next_active = [&](Window& w, int i) -> int {
     if (!masked) return i < P.n_q_tiles ? (i | (dense ? kMixedBit : 0)) : P.n_q_tiles;
-    for (; i < P.n_q_tiles; i += 32) {
-      const int t = i + lane;
-      int cls = 0;  // 0 skip, 1 all visible, 2 mixed; +4 contiguous positions
-      if (t < P.n_q_tiles) {
-        const TileMeta mq = P.meta_q[bb * P.n_q_tiles + t];
-        cls = classify_tiles(kinds, p.mod.window, mq, mk) | (mq.pos_contig ? 4 : 0);
+    while (i < P.n_q_tiles) {
+      if (i < w.base || i >= w.base + 32) {
+        w.base = i;
+        w.cls = 0;
+        const int t = i + lane;
+        if (t < P.n_q_tiles) {
+          const TileMeta mq = P.meta_q[bb * P.n_q_tiles + t];
+          w.cls = classify_tiles(kinds, p.mod.window, mq, mk) | (mq.pos_contig ? 4 : 0);
+          w.pos0 = mq.pos_min;
+        }
       }
-      const uint32_t vote = __ballot_sync(0xffffffffu, (cls & 3) != 0);
+      const uint32_t vote = __ballot_sync(0xffffffffu, (w.cls & 3) != 0 && lane >= i - w.base);
       if (vote) {
         const int first = __ffs(vote) - 1;
-        const int c = __shfl_sync(0xffffffffu, cls, first);
-        return (i + first) | (((c & 3) == 2 || dense) ? kMixedBit : 0) | ((c & 4) ? kContigBit : 0);
+        const int c = __shfl_sync(0xffffffffu, w.cls, first);
+        w.hit_pos0 = __shfl_sync(0xffffffffu, w.pos0, first);
+        return (w.base + first) | (((c & 3) == 2 || dense) ? kMixedBit : 0) | ((c & 4) ? kContigBit : 0);
       }
+      i = w.base + 32;
     }
     return P.n_q_tiles;
   };
@@ -169,7 +192,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       prefetch_tensormap(&P.map_do);
       if constexpr (D == 128) prefetch_tensormap(&P.map_dq);
     }
-    const int i = next_active(0) & kTileIdx;
+    Window wq, wdo;
+    const int i = next_active(wq, 0) & kTileIdx;
     if (i < P.n_q_tiles && lane == 0) {
       mbar_arrive_expect_tx(&bars[KV_FULL], 2 * TILE_BYTES);
       for (int pn = 0; pn < PANELS; ++pn) {
@@ -197,10 +221,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           mbar_arrive_expect_tx(&bars[Q_FULL0 + s], TILE_BYTES + 2 * kTileRows * 4);
           for (int pn = 0; pn < PANELS; ++pn)
             tma_load_4d(sQ + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_q, &bars[Q_FULL0 + s], pn * 64, hh, qi * kTileRows, bb);
-          bulk_load(sL + s * kTileRows, p.lse + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
-          bulk_load(sDelta + s * kTileRows, p.delta + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
+          bulk_load(sL + s * kTileRows, p.row_nl2 + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
+          bulk_load(sDelta + s * kTileRows, p.row_nds + row_base + (int64_t)qi * kTileRows, kTileRows * 4, &bars[Q_FULL0 + s]);
         }
-        qi = next_active(qi + 1) & kTileIdx;
+        qi = next_active(wq, qi + 1) & kTileIdx;
         ++qn;
       }
       if (ready & 2u) {
@@ -210,7 +234,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           for (int pn = 0; pn < PANELS; ++pn)
             tma_load_4d(sdO + s * TILE_BYTES + pn * PANEL_BYTES, &P.map_do, &bars[DO_FULL0 + s], pn * 64, hh, doi * kTileRows, bb);
         }
-        doi = next_active(doi + 1) & kTileIdx;
+        doi = next_active(wdo, doi + 1) & kTileIdx;
         ++don;
       }
       if (ready) {
@@ -280,7 +304,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       // so that the compute warps form P(n+1) under dQ(n)/dK(n), drain dQ(n) under dK(n), and
       // form dS(n+1) under dV(n+1)/S(n+2).
       bool ok = true;
-      int i = next_active(0) & kTileIdx;
+      Window win;
+      int i = next_active(win, 0) & kTileIdx;
       if (i < P.n_q_tiles) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
                                          mbar_wait(&bars[Q_FULL0], 0, abort_flag, P.status, kStBwdMma) &&
@@ -301,7 +326,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           const int dsn = (n + 1) % DO_ST;  // dO stage and phase of tile n + 1
           const uint32_t dphn = ((n + 1) / DO_ST) & 1;
           const uint32_t par = n & 1;
-          const int inext = next_active(i + 1) & kTileIdx;
+          const int inext = next_active(win, i + 1) & kTileIdx;
           const bool has_next = inext < P.n_q_tiles;
           if (has_next) {
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL0 + sn], ((n + 1) >> 1) & 1, abort_flag, P.status, kStBwdMma)))) break;
@@ -365,23 +390,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     uint32_t sv[2][32];
     const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
     const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
-    // first query position of a tile, read one tile ahead like the tile class
-    auto first_qpos = [&](int e) -> int32_t {
-      return (p.mod.q_pos && (e & kTileIdx) < P.n_q_tiles) ? p.mod.q_pos[(int64_t)bb * p.lq + (int64_t)(e & kTileIdx) * kTileRows] : 0;
-    };
+    Window win;
 
     // One loop body serves every tile so that each phase exists once in the instruction
     // stream: step k does dS^T(k-1), then P^T(k), then the dQ drain of tile k-1.
-    int i_prev = -1, e_cur = next_active(0), i_cur = e_cur & kTileIdx;
-    int32_t q0_cur = first_qpos(e_cur);
+    int i_prev = -1, e_cur = next_active(win, 0), i_cur = e_cur & kTileIdx;
+    int32_t q0_cur = win.hit_pos0;  // first query position of the tile (used when its positions are contiguous)
     for (int k = 0; ok; ++k) {
       const bool have_prev = k > 0, have_cur = i_cur < P.n_q_tiles;
       if (!have_prev && !have_cur) break;
-      // looked up here so that the load's latency passes under the work below
-      const int e_next = have_cur ? next_active(i_cur + 1) : P.n_q_tiles;
-      const int32_t q0_next = first_qpos(e_next);
+      const int e_next = have_cur ? next_active(win, i_cur + 1) : P.n_q_tiles;
+      const int32_t q0_next = win.hit_pos0;
       if (have_prev) {
-        // ---- dS^T = P^T * (dP^T - delta) of tile k-1 -> shared memory, 128-byte swizzle
+        // ---- dS^T = P^T * (dP^T * scale - delta * scale) of tile k-1 -> shared memory, 128-byte swizzle
         const int n = k - 1, s = n & 1;
         const float4* Dls = reinterpret_cast<const float4*>(sDelta + s * kTileRows + g * 64);
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
@@ -391,16 +412,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         tc_wait_ld();
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_FREE], (n & 1) ^ 1, abort_flag, P.status, kStBwdCompute)))) break;
         uint8_t* row_ptr = sdS + g * PANEL_BYTES + r * 128;
+        const uint64_t scl2 = pack2(p.scale, p.scale);
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
-          const float4 da = Dls[ch * 2], db = Dls[ch * 2 + 1];
-          const float dl[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+          const float4 da = Dls[ch * 2], db = Dls[ch * 2 + 1];  // -delta * scale of 8 queries
+          const uint64_t dl2[4] = {pack2(da.x, da.y), pack2(da.z, da.w), pack2(db.x, db.y), pack2(db.z, db.w)};
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = ch * 8 + e * 2;
-            const float d0 = pf[c] * (__uint_as_float(sv[c >> 5][c & 31]) - dl[e * 2]);
-            const float d1 = pf[c + 1] * (__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]) - dl[e * 2 + 1]);
+            const uint64_t dp2 = pack2(__uint_as_float(sv[c >> 5][c & 31]), __uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]));
+            float d0, d1;
+            unpack2(mul2(pack2(pf[c], pf[c + 1]), fma2(dp2, scl2, dl2[e])), d0, d1);
             w[e] = pack_bf16(d0, d1);
           }
           *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -444,18 +467,42 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
             sv[c >> 5][c & 31] = __float_as_uint(fmaf(-slope2, (float)c, fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, rr)));
           sc = 1.f;
         }
+        if (dense) {
+          // With a dense bias tile the reference's arithmetic is kept as it is (ring.py:146): a row
+          // whose L is -inf (it saw no key) gives exp(-inf + inf) = NaN.
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 lv = Ls[c4];
-          const float l4[4] = {lv.x, lv.y, lv.z, lv.w};
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const float4 lv = Ls[c4];
+            const float l4[4] = {lv.x, lv.y, lv.z, lv.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = c4 * 4 + e;
-            // a masked pair (-inf) gives exp2(-inf) = 0; the clamp keeps a row whose L is -inf
-            // (it saw no key) from turning that into exp2(-inf + inf).  With a dense bias tile
-            // the reference's arithmetic is kept as it is (ring.py:146): such a row gives NaN.
-            const float neg_l2 = dense ? -l4[e] * kLog2e : fminf(-l4[e] * kLog2e, 1e30f);
-            pf[c] = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, neg_l2));
+            for (int e = 0; e < 4; ++e) {
+              const int c = c4 * 4 + e;
+              pf[c] = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, l4[e]));  // l4: -L * log2(e), unclamped
+            }
+          }
+        } else {
+          // A masked pair (-inf) gives exp2(-inf) = 0; the clamp in the row term keeps a row whose L
+          // is -inf from turning that into exp2(-inf + inf).  Column pairs: packed arithmetic, and the first
+          // kBwdPolyPairs of every 16 pairs take the exponential from the FMA-pipe polynomial.
+          const uint64_t sc2 = pack2(sc, sc);
+#pragma unroll
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const float4 lv = Ls[c4];
+            const float l4[4] = {lv.x, lv.y, lv.z, lv.w};
+#pragma unroll
+            for (int e = 0; e < 4; e += 2) {
+              const int c = c4 * 4 + e;
+              const uint64_t nl2 = pack2(l4[e], l4[e + 1]);  // min(-L * log2(e), 1e30) of the two queries
+              const uint64_t x2 = fma2(pack2(__uint_as_float(sv[c >> 5][c & 31]), __uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31])), sc2, nl2);
+              if (((c >> 1) & 15) < kBwdPolyPairs) {
+                exp2_poly2(x2, pf[c], pf[c + 1]);
+              } else {
+                float x0, x1;
+                unpack2(x2, x0, x1);
+                pf[c] = ex2(x0);
+                pf[c + 1] = ex2(x1);
+              }
+            }
           }
         }
         uint32_t pk[32];
@@ -480,22 +527,25 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           // next tile does not wait for what follows
           tc_fence_before();
           mbar_arrive(&bars[DQ_DRAINED]);
-          // 4 rounds of 16 queries through this warp's two staging buffers; the TMA unit adds
-          // each [16 queries][32 lanes] box to the accumulator rows
-          float* stage = sdQ + warp * (2 * 16 * 32);
+          // 4 rounds of 16 queries through this warpgroup's two staging buffers; the TMA unit adds
+          // each [16 queries][128 head-dim lanes] box (8 KB) to the accumulator rows.  One thread
+          // of the warpgroup issues; few large reduce-adds, not many small ones: the TMA unit's
+          // rate of operations, not its bytes, is what the small boxes ran into.
+          float* stage = sdQ + g * (2 * 16 * 128);
           const int dq_row0 = (int)(qrow_base + (int64_t)i_prev * kTileRows + g * 64);
+          const bool issuer = (warp & 3) == 0 && lane == 0;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            float* buf = stage + (j & 1) * (16 * 32);
-            if (lane == 0) bulk_wait_group_read<1>();  // the reduce issued two rounds ago has read this buffer
-            __syncwarp();
+            float* buf = stage + (j & 1) * (16 * 128);
+            if (issuer) bulk_wait_group_read<1>();  // the reduce issued two rounds ago has read this buffer
+            named_bar_sync(1 + g, 128);
 #pragma unroll
             for (int c = 0; c < 16; ++c)
-              buf[c * 32 + lane] = __uint_as_float(sv[(j * 16 + c) >> 5][(j * 16 + c) & 31]) * p.scale;
+              buf[c * 128 + r] = __uint_as_float(sv[(j * 16 + c) >> 5][(j * 16 + c) & 31]);
             fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_2d(&P.map_dq, buf, (warp & 3) * 32, dq_row0 + j * 16);
+            named_bar_sync(1 + g, 128);
+            if (issuer) {
+              tma_reduce_add_2d(&P.map_dq, buf, 0, dq_row0 + j * 16);
               bulk_commit_group();
             }
           }
@@ -506,8 +556,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           tc_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq_row + e, __uint_as_float(sv[0][e]) * p.scale, __uint_as_float(sv[0][e + 1]) * p.scale,
-                       __uint_as_float(sv[0][e + 2]) * p.scale, __uint_as_float(sv[0][e + 3]) * p.scale);
+            red_add_v4(dq_row + e, __uint_as_float(sv[0][e]), __uint_as_float(sv[0][e + 1]), __uint_as_float(sv[0][e + 2]),
+                       __uint_as_float(sv[0][e + 3]));
           tc_fence_before();
           mbar_arrive(&bars[DQ_DRAINED]);
         }
@@ -542,19 +592,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         tc_wait_ld();
         if (direct) {
           uint4 w;
-          w.x = pack_bf16(__uint_as_float(a[0]) * p.scale, __uint_as_float(a[1]) * p.scale);
-          w.y = pack_bf16(__uint_as_float(a[2]) * p.scale, __uint_as_float(a[3]) * p.scale);
-          w.z = pack_bf16(__uint_as_float(a[4]) * p.scale, __uint_as_float(a[5]) * p.scale);
-          w.w = pack_bf16(__uint_as_float(a[6]) * p.scale, __uint_as_float(a[7]) * p.scale);
+          w.x = pack_bf16(__uint_as_float(a[0]), __uint_as_float(a[1]));
+          w.y = pack_bf16(__uint_as_float(a[2]), __uint_as_float(a[3]));
+          w.z = pack_bf16(__uint_as_float(a[4]), __uint_as_float(a[5]));
+          w.w = pack_bf16(__uint_as_float(a[6]), __uint_as_float(a[7]));
           *reinterpret_cast<uint4*>(dk_o + c * 8) = w;
         } else {
 #pragma unroll
           for (int e = 0; e < 8; e += 4) {
             float4 cur = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<float4*>(dk_row + c * 8 + e);
-            cur.x += __uint_as_float(a[e]) * p.scale;
-            cur.y += __uint_as_float(a[e + 1]) * p.scale;
-            cur.z += __uint_as_float(a[e + 2]) * p.scale;
-            cur.w += __uint_as_float(a[e + 3]) * p.scale;
+            cur.x += __uint_as_float(a[e]);
+            cur.y += __uint_as_float(a[e + 1]);
+            cur.z += __uint_as_float(a[e + 2]);
+            cur.w += __uint_as_float(a[e + 3]);
             *reinterpret_cast<float4*>(dk_row + c * 8 + e) = cur;
           }
         }
@@ -603,7 +653,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     }
     // the staging buffers must outlive the reduce-adds that read them
     if constexpr (D == 128) {
-      if (lane == 0) bulk_wait_group<0>();
+      if ((warp & 3) == 0 && lane == 0) bulk_wait_group<0>();
     }
   }
 
@@ -669,7 +719,7 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
       !make_tile_map(&P.map_do, p.dout, p.b, p.lq, p.h, p.dv_dim, kTileRows, &why))
     return cudaErrorNotSupported;
   if (p.dk_dim == 128 &&
-      !make_f32_rows_map(&P.map_dq, p.dq, (int64_t)p.b * p.h * p.lq, 128, 32, 16, &why))
+      !make_f32_rows_map(&P.map_dq, p.dq, (int64_t)p.b * p.h * p.lq, 128, 128, 16, &why))
     return cudaErrorNotSupported;
   P.status = device_status_word();
   if (!P.status) return cudaErrorInvalidSymbol;
@@ -681,10 +731,24 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
   if (group > (int64_t)p.b * p.h) group = (int64_t)p.b * p.h;
   P.group_heads = (int)group;
   TileMeta* meta = nullptr;
+  float* terms = nullptr;
   cudaError_t e = cudaSuccess;
-  if (p.mod.kinds & kMetaKinds) {
+  if (!p.row_nl2 || !p.row_nds) {  // block-level callers pass L and delta as the reference does
+    const int64_t rows = (int64_t)p.b * p.h * p.lq;
+    const size_t each = ((size_t)rows * sizeof(float) + 255) / 256 * 256;
+    if ((e = scratch_alloc((void**)&terms, 2 * each, s)) != cudaSuccess) return e;
+    float* nl2 = terms;
+    float* nds = reinterpret_cast<float*>(reinterpret_cast<char*>(terms) + each);
+    e = launch_bwd_row_terms(p.lse, p.delta, p.scale, (p.mod.kinds & RA_MOD_DENSE) ? 0 : 1, rows, nl2, nds, s);
+    P.p.row_nl2 = nl2;
+    P.p.row_nds = nds;
+  }
+  if (e == cudaSuccess && (p.mod.kinds & kMetaKinds)) {
     const size_t n = (size_t)p.b * (P.n_q_tiles + P.n_kv_tiles);
-    if ((e = scratch_alloc((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) return e;
+    if ((e = scratch_alloc((void**)&meta, n * sizeof(TileMeta), s)) != cudaSuccess) {
+      if (terms) cudaFreeAsync(terms, s);
+      return e;
+    }
     TileMeta* mq = meta;
     TileMeta* mk = meta + (size_t)p.b * P.n_q_tiles;
     if ((e = launch_tile_meta(mq, p.mod.q_pos, p.mod.q_seg, p.mod.q_pre, p.b, p.lq, s)) == cudaSuccess)
@@ -694,6 +758,7 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
   }
   if (e == cudaSuccess) e = p.dk_dim == 128 ? launch_bwd<128>(P, s) : launch_bwd<64>(P, s);
   if (meta) cudaFreeAsync(meta, s);  // stream-ordered: after the kernels above, also when one failed to launch
+  if (terms) cudaFreeAsync(terms, s);
   return e;
 }
 

@@ -48,6 +48,13 @@ struct BwdParams {
   ModParams mod;
   const float* lse;    // [b,h,lq]
   const float* delta;  // [b,h,lq]
+  // Optional, read by the tcgen05 kernel instead of lse / delta when set: the per-row terms of
+  // its inner loops, computed once per backward instead of once per tile and thread:
+  //   row_nl2 = min(-lse * log2(e), 1e30)  (no clamp with a dense bias tile: ring.py:146 as it is)
+  //   row_nds = -delta * scale
+  // When they are NULL the launcher derives them into scratch first.
+  const float* row_nl2;
+  const float* row_nds;
   float* dq;           // [b,h,lq,dk] fp32, accumulated with atomics
   float* dk;           // [b,h,lk,dk] fp32, += per call
   float* dv;           // [b,h,lk,dv] fp32, += per call
@@ -75,7 +82,12 @@ cudaError_t launch_delta(int b, int h, int lq, int dv, TensorView out, TensorVie
                          float* delta, cudaStream_t s);
 cudaError_t launch_cast_from_f32(int b, int h, int len, int d, const float* src, TensorView dst,
                                  int dtype, cudaStream_t s);
+// nl2[i] = min(-lse[i] * log2(e), 1e30) (clamp left out when !clamp), nds[i] = -delta[i] * scale.
+cudaError_t launch_bwd_row_terms(const float* lse, const float* delta, float scale, int clamp, int64_t n, float* nl2,
+                                 float* nds, cudaStream_t s);
 cudaError_t launch_add_f32(float* dst, const float* src, int64_t n, cudaStream_t s);
+// dst[seg * pitch + i] += src[seg * pitch + i] for seg < nseg, i < seg_elems (a multiple of 4; 16-byte aligned rows).
+cudaError_t launch_add_rows_f32(float* dst, const float* src, int64_t nseg, int64_t seg_elems, int64_t pitch, cudaStream_t s);
 // One block per (batch, head): where some query row has L = -inf, dq of those rows and all of
 // dk, dv of that (batch, head) become NaN (what ring.py:146 produces for such rows).
 cudaError_t launch_strict_nan(int b, int h, int lq, int lk, int dk_dim, int dv_dim, const float* lse, float* dq,

@@ -125,6 +125,17 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
       if (active) list[cnt + __popc(vote & ((1u << lane) - 1))] = (uint16_t)(j | (code << 12));
       cnt += __popc(vote);
     }
+    // ALiBi makes the scores grow towards the query's own position: visiting the K/V tiles in
+    // ascending order would raise the running max (and rescale O) at nearly every tile for the
+    // steeper heads.  Nearest tiles first: the max is found early.  Only the order changes.
+    if ((kinds & RA_MOD_ALIBI) && !(kinds & RA_MOD_DENSE)) {
+      __syncwarp();
+      for (int i = lane; i < cnt / 2; i += 32) {
+        const uint16_t a = list[i], z = list[cnt - 1 - i];
+        list[i] = z;
+        list[cnt - 1 - i] = a;
+      }
+    }
     if (lane == 0) *count_slot = cnt;
   }
   tc_fence_before();
@@ -300,13 +311,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1) tc_fwd_kernel(const __grid_con
         alpha_total *= alpha;
         if (i > 0) {  // O of this tile holds the sum over the tiles before this one
 #pragma unroll 1
-          for (int c = 0; c < D / 8; ++c) {
-            uint32_t o[8];
-            tmem_ld8(tmem_O[t] + lane_off + c * 8, o);
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld16(tmem_O[t] + lane_off + c * 16, o);
             tc_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st8(tmem_O[t] + lane_off + c * 8, o);
+            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st16(tmem_O[t] + lane_off + c * 16, o);
           }
         }
       }

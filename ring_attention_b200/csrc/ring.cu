@@ -205,9 +205,14 @@ struct IpcBundle {
 using namespace ringimpl;
 
 // Which (query shard, K/V block) pairs of the ring have a visible pair at all: need[q_rank * n + kv_rank].
+// rows: for every pair, up to two runs of K/V rows (one in each half of the block: a zig-zag
+// shard is two position-contiguous halves) outside which the queries of q_rank see nothing,
+// in 128-row chunks: rows[((q_rank * n + kv_rank) * 2 + half) * 2 + {0: first, 1: one past last}].
 struct ra_ring_plan {
   int nranks = 1;
+  int lk = 0;  // K/V rows per block the row runs were computed for (0: no runs, whole blocks move)
   std::vector<uint8_t> need;
+  std::vector<int32_t> rows;
 };
 
 struct ra_ring {
@@ -307,22 +312,42 @@ __global__ void plan_meta_kernel(TileMeta* __restrict__ out, const int32_t* __re
   }
 }
 
-// all: [nranks][b * (nq + nk)] summaries, the q chunks of a rank first.  need[r * nranks + o] = 1 when
-// some query chunk of rank r and some K/V chunk of rank o (same batch element) are not fully masked.
+// all: [nranks][b * (nq + nk)] summaries, the q chunks of a rank first.  For the pair (r, o) =
+// (blockIdx.x / nranks, blockIdx.x % nranks): need = 1 when some query chunk of rank r and some
+// K/V chunk of rank o (same batch element) are not fully masked, and rows[pair][half] = the run
+// [first, one past last] of such K/V chunks in each half of the block (over all batch elements).
 __global__ void plan_need_kernel(const TileMeta* __restrict__ all, int nranks, int b, int nq, int nk, uint32_t kinds,
-                                 int32_t window, int* __restrict__ need) {
+                                 int32_t window, int* __restrict__ need, int32_t* __restrict__ rows) {
   const int r = blockIdx.x / nranks, o = blockIdx.x % nranks;
   const int64_t per_rank = (int64_t)b * (nq + nk);
   const TileMeta* mq = all + r * per_rank;
   const TileMeta* mk = all + o * per_rank + (int64_t)b * nq;
-  int found = 0;
-  const int64_t total = (int64_t)b * nq * nk;
-  for (int64_t i = threadIdx.x; i < total && !found; i += blockDim.x) {
-    const int bb = (int)(i / ((int64_t)nq * nk));
-    const int rem = (int)(i % ((int64_t)nq * nk));
-    if (classify_tiles(kinds, window, mq[bb * nq + rem / nk], mk[bb * nk + rem % nk]) != 0) found = 1;
+  __shared__ int s_lo[2], s_hi[2];
+  if (threadIdx.x < 2) {
+    s_lo[threadIdx.x] = INT32_MAX;
+    s_hi[threadIdx.x] = 0;
   }
-  if (__syncthreads_or(found) && threadIdx.x == 0) need[blockIdx.x] = 1;
+  __syncthreads();
+  const int half_at = (nk + 1) / 2;
+  for (int i = threadIdx.x; i < b * nk; i += blockDim.x) {
+    const int bb = i / nk, kc = i % nk;
+    const TileMeta k = mk[bb * nk + kc];
+    bool seen = false;
+    for (int qc = 0; qc < nq && !seen; ++qc) seen = classify_tiles(kinds, window, mq[bb * nq + qc], k) != 0;
+    if (seen) {
+      const int half = kc >= half_at ? 1 : 0;
+      atomicMin(&s_lo[half], kc);
+      atomicMax(&s_hi[half], kc + 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    need[blockIdx.x] = (s_hi[0] > 0 || s_hi[1] > 0) ? 1 : 0;
+    for (int half = 0; half < 2; ++half) {
+      rows[blockIdx.x * 4 + half * 2] = s_hi[half] > 0 ? s_lo[half] : 0;
+      rows[blockIdx.x * 4 + half * 2 + 1] = s_hi[half];
+    }
+  }
 }
 
 struct KvMessage {
@@ -331,23 +356,40 @@ struct KvMessage {
   const void* src[5];
   size_t bytes[5];
   size_t offset[5];
+  // parts that are [b][lk rows][row_bytes] and may travel as row runs: bytes of one row (0: the
+  // part always travels whole) and number of batch elements
+  size_t row_bytes[5];
+  int nb[5];
   int n = 0;
   size_t total = 0;
-  void add(const void* p, size_t nbytes) {
+  void add(const void* p, size_t nbytes, size_t row = 0, int batches = 1) {
     src[n] = p;
     bytes[n] = nbytes;
     offset[n] = total;
+    row_bytes[n] = row;
+    nb[n] = batches;
     total += align_up(nbytes);
     ++n;
   }
+};
+
+// Up to two runs of K/V rows of one block.
+struct RowRuns {
+  int n = 1;
+  int lo[2] = {0, 0}, hi[2] = {0, 0};
 };
 
 KvMessage make_kv_message(const ra_shape_t* sh, const TensorView& k, const TensorView& v,
                           const ModParams& mod) {
   KvMessage msg;
   size_t es = sh->dtype == RA_DTYPE_F32 ? 4 : 2;
-  msg.add(k.ptr, (size_t)sh->b * sh->lk * sh->h * sh->dk * es);
-  msg.add(v.ptr, (size_t)sh->b * sh->lk * sh->h * sh->dv * es);
+  // row runs need rows that are contiguous and batch elements one block of rows apart: [b, l, h, d]
+  auto blhd = [&](const TensorView& t, int d) {
+    return (sh->h == 1 || t.sh == d) && (sh->lk == 1 || t.sl == (int64_t)sh->h * d) &&
+           (sh->b == 1 || t.sb == (int64_t)sh->lk * sh->h * d);
+  };
+  msg.add(k.ptr, (size_t)sh->b * sh->lk * sh->h * sh->dk * es, blhd(k, sh->dk) ? (size_t)sh->h * sh->dk * es : 0, sh->b);
+  msg.add(v.ptr, (size_t)sh->b * sh->lk * sh->h * sh->dv * es, blhd(v, sh->dv) ? (size_t)sh->h * sh->dv * es : 0, sh->b);
   size_t tok = (size_t)sh->b * sh->lk;
   if (mod.kv_pos) msg.add(mod.kv_pos, tok * 4);
   if (mod.kv_seg) msg.add(mod.kv_seg, tok * 4);
@@ -598,12 +640,33 @@ int ensure_shared(ra_ring_t* r, size_t stage_need, size_t rpart_need) {
 }
 
 // to / from < 0: that half of the exchange is left out (both ends of it agree, see pair_needed)
-int exchange_kv_nccl(ra_ring_t* r, const KvMessage& msg, void* stage, int to, int from) {
+RowRuns pair_rows(const ra_ring_t* r, int q_rank, int kv_rank, int lk);
+
+// One side (send or receive) of a K/V message over NCCL: whole parts, or one message per row
+// run and batch element.  Both ends derive the same runs from the same plan.
+int nccl_part(ra_ring_t* r, const KvMessage& msg, int i, char* base, const RowRuns& rr, int lk, int peer, bool send) {
   NcclApi* api = nccl_api();
+  const size_t rb = msg.row_bytes[i];
+  auto one = [&](char* p, size_t n) -> int {
+    if (send) RA_NCCL(api->Send(p, n, ncclChar, peer, r->comm, r->push_stream), "ncclSend");
+    else RA_NCCL(api->Recv(p, n, ncclChar, peer, r->comm, r->push_stream), "ncclRecv");
+    return 0;
+  };
+  if (rb == 0 || (rr.n == 1 && rr.lo[0] == 0 && rr.hi[0] == lk)) return one(base, msg.bytes[i]);
+  int rc;
+  for (int bb = 0; bb < msg.nb[i]; ++bb)
+    for (int k = 0; k < rr.n; ++k)
+      if ((rc = one(base + ((size_t)bb * lk + rr.lo[k]) * rb, (size_t)(rr.hi[k] - rr.lo[k]) * rb))) return rc;
+  return 0;
+}
+
+int exchange_kv_nccl(ra_ring_t* r, const KvMessage& msg, void* stage, int to, int from, int lk) {
+  NcclApi* api = nccl_api();
+  int rc;
   RA_NCCL(api->GroupStart(), "ncclGroupStart");
   for (int i = 0; i < msg.n; ++i) {
-    if (to >= 0) RA_NCCL(api->Send(msg.src[i], msg.bytes[i], ncclChar, to, r->comm, r->push_stream), "ncclSend");
-    if (from >= 0) RA_NCCL(api->Recv((char*)stage + msg.offset[i], msg.bytes[i], ncclChar, from, r->comm, r->push_stream), "ncclRecv");
+    if (to >= 0 && (rc = nccl_part(r, msg, i, (char*)const_cast<void*>(msg.src[i]), pair_rows(r, to, r->rank, lk), lk, to, true))) return rc;
+    if (from >= 0 && (rc = nccl_part(r, msg, i, (char*)stage + msg.offset[i], pair_rows(r, r->rank, from, lk), lk, from, false))) return rc;
   }
   RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
   return 0;
@@ -617,7 +680,51 @@ bool pair_needed(const ra_ring_t* r, int q_rank, int kv_rank) {
   return !r->plan || r->ignore_plan || r->plan->need[(size_t)q_rank * r->nranks + kv_rank] != 0;
 }
 
-int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
+// The rows of kv_rank's block that the queries of q_rank see something in: whole block without a
+// plan (or when the plan was made for another block length).
+RowRuns pair_rows(const ra_ring_t* r, int q_rank, int kv_rank, int lk) {
+  RowRuns rr;
+  rr.hi[0] = lk;
+  const ra_ring_plan* pl = r->plan;
+  if (!pl || r->ignore_plan || pl->lk != lk || pl->rows.empty()) return rr;
+  const int32_t* w = &pl->rows[((size_t)q_rank * r->nranks + kv_rank) * 4];
+  rr.n = 0;
+  for (int half = 0; half < 2; ++half) {
+    int lo = w[half * 2] * 128, hi = w[half * 2 + 1] * 128;
+    if (hi > lk) hi = lk;
+    if (lo >= hi) continue;
+    if (rr.n > 0 && rr.hi[rr.n - 1] == lo) {
+      rr.hi[rr.n - 1] = hi;  // the two runs touch: one copy
+    } else {
+      rr.lo[rr.n] = lo;
+      rr.hi[rr.n] = hi;
+      ++rr.n;
+    }
+  }
+  return rr;
+}
+
+// Copies one part of a K/V message into a peer's staging buffer: whole, or its row runs.
+int push_part(ra_ring_t* r, const KvMessage& msg, int i, void* dst_base, const RowRuns& rr, int lk, double* sent) {
+  char* dst = (char*)dst_base + msg.offset[i];
+  const char* src = (const char*)msg.src[i];
+  const size_t rb = msg.row_bytes[i];
+  if (rb == 0 || (rr.n == 1 && rr.lo[0] == 0 && rr.hi[0] == lk)) {
+    RA_CUDA(cudaMemcpyAsync(dst, src, msg.bytes[i], cudaMemcpyDeviceToDevice, r->push_stream), "cudaMemcpyAsync(peer K/V)");
+    *sent += (double)msg.bytes[i];
+    return 0;
+  }
+  const size_t pitch = (size_t)lk * rb;
+  for (int k = 0; k < rr.n; ++k) {
+    const size_t off = (size_t)rr.lo[k] * rb, width = (size_t)(rr.hi[k] - rr.lo[k]) * rb;
+    RA_CUDA(cudaMemcpy2DAsync(dst + off, pitch, src + off, pitch, width, msg.nb[i], cudaMemcpyDeviceToDevice, r->push_stream),
+            "cudaMemcpy2DAsync(peer K/V rows)");
+    *sent += (double)width * msg.nb[i];
+  }
+  return 0;
+}
+
+int send_kv(ra_ring_t* r, const KvMessage& msg, int t, int lk) {
   const int N = r->nranks, me = r->rank, slot = t & 1;
   const int to = (me + t) % N, from = ((me - t) % N + N) % N;
   const bool do_send = pair_needed(r, to, me), do_recv = pair_needed(r, me, from);
@@ -628,17 +735,16 @@ int send_kv(ra_ring_t* r, const KvMessage& msg, int t) {
     int rc;
     if ((rc = launch_wait(r, r->push_stream, progress_flag(slot, to), need))) return rc;
     double sent = 0;
-    for (int i = 0; i < msg.n; ++i) sent += (double)msg.bytes[i];
-    if ((rc = push_mark(r, r->push_stream, sent))) return rc;
-    for (int i = 0; i < msg.n; ++i)
-      RA_CUDA(cudaMemcpyAsync((char*)r->peers[to].stage[slot] + msg.offset[i], msg.src[i], msg.bytes[i],
-                              cudaMemcpyDeviceToDevice, r->push_stream), "cudaMemcpyAsync(peer K/V)");
+    const RowRuns rr = pair_rows(r, to, me, lk);  // what the consumer's queries see of this rank's block
     if ((rc = push_mark(r, r->push_stream, 0))) return rc;
+    for (int i = 0; i < msg.n; ++i)
+      if ((rc = push_part(r, msg, i, r->peers[to].stage[slot], rr, lk, &sent))) return rc;
+    if ((rc = push_mark(r, r->push_stream, sent))) return rc;
     return launch_set(r, r->push_stream, to, kFlagKvReady + slot, r->epoch + t);
   }
   if (t >= 2) RA_CUDA(cudaStreamWaitEvent(r->push_stream, r->ev_done[slot], 0), "cudaStreamWaitEvent");
   int rc;
-  if ((do_send || do_recv) && (rc = exchange_kv_nccl(r, msg, r->stage[slot], do_send ? to : -1, do_recv ? from : -1))) return rc;
+  if ((do_send || do_recv) && (rc = exchange_kv_nccl(r, msg, r->stage[slot], do_send ? to : -1, do_recv ? from : -1, lk))) return rc;
   RA_CUDA(cudaEventRecord(r->ev_recv[slot], r->push_stream), "cudaEventRecord");
   return 0;
 }
@@ -1028,7 +1134,7 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   for (int t = 0; t < N; ++t) {
     const int ln = t & (n_lanes - 1);
     cudaStream_t s = lane_s[ln];
-    if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;  // runs under step t
+    if (t + 1 < N && (rc = send_kv(ring, msg, t + 1, shape->lk))) return rc;  // runs under step t
     if (t > 0 && !pair_needed(ring, me_f, source(t))) {  // nothing visible in this block: no wait, no launch
       if ((rc = step_done(ring, t, s))) return rc;
       continue;
@@ -1089,6 +1195,8 @@ BwdParams sub_problem(const BwdParams& p, int esize, int b0, int nb, int h0, int
   const int64_t bh0 = (int64_t)b0 * p.h + h0;
   s.lse = p.lse + bh0 * p.lq;
   s.delta = p.delta + bh0 * p.lq;
+  if (p.row_nl2) s.row_nl2 = p.row_nl2 + bh0 * p.lq;
+  if (p.row_nds) s.row_nds = p.row_nds + bh0 * p.lq;
   s.dq = p.dq + bh0 * p.lq * p.dk_dim;
   s.dk = p.dk + bh0 * p.lk * p.dk_dim;
   s.dv = p.dv + bh0 * p.lk * p.dv_dim;
@@ -1138,8 +1246,11 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   const bool split_b = z.split_b, split_h = z.split_h, split = split_b || split_h;
   const int b0 = z.b0, h0 = z.h0, nb2 = z.nb2, nh2 = z.nh2;
   const size_t rows2 = z.rows2, own2_dk_b = z.own2_dk_b, own2_dv_b = z.own2_dv_b;
-  RA_CUDA(ring->grads.reserve(delta_b + dq_b + dk_b + dv_b + own2_dk_b + own2_dv_b), "cudaMalloc(grads)");
-  char* g = (char*)ring->grads.ptr;
+  // delta, then the two per-row terms derived from L and delta that the tensor-core kernel reads
+  RA_CUDA(ring->grads.reserve(3 * delta_b + dq_b + dk_b + dv_b + own2_dk_b + own2_dv_b), "cudaMalloc(grads)");
+  char* g = (char*)ring->grads.ptr + 2 * delta_b;
+  float* row_nl2 = (float*)ring->grads.ptr;
+  float* row_nds = (float*)((char*)ring->grads.ptr + delta_b);
   float* delta = (float*)g;
   float* dq_acc = (float*)(g + delta_b);
   float* dk_acc = (float*)(g + delta_b + dq_b);
@@ -1159,6 +1270,12 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
                                shape->dtype, delta, stream);
   if (e != cudaSuccess) return fail_cuda(e, "delta");
   p.delta = delta;
+  if (current_impl() != RA_IMPL_SIMT) {  // once per backward, not once per block launch
+    e = launch_bwd_row_terms(lse, delta, shape->sm_scale, 1, (int64_t)shape->b * shape->h * shape->lq, row_nl2, row_nds, stream);
+    if (e != cudaSuccess) return fail_cuda(e, "row terms");
+    p.row_nl2 = row_nl2;
+    p.row_nds = row_nds;
+  }
   p.dq = dq_acc;
   // Ring of one on the tensor-core path: the kernel stores dK, dV in the result dtype itself, so
   // their fp32 accumulators are neither cleared nor converted.
@@ -1205,7 +1322,7 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   const ModParams mod_own = p.mod;
   for (int t = 0; t < N; ++t) {
     cudaStream_t s = lane_s[t & 1];
-    if (t + 1 < N && (rc = send_kv(ring, msg, t + 1))) return rc;
+    if (t + 1 < N && (rc = send_kv(ring, msg, t + 1, shape->lk))) return rc;
     p.k = k_own;
     p.v = v_own;
     p.mod = mod_own;
@@ -1228,6 +1345,10 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     // Under a plan: this rank computes (and gives) only where its queries see the block, and
     // receives only where the giver's queries see this rank's block.
     const bool compute = pair_needed(ring, me, owner), receive = pair_needed(ring, giver, me);
+    // key rows of the contribution this rank gives (those its queries saw in the owner's block)
+    // and of the one it receives (those the giver's queries saw in this rank's block)
+    const RowRuns give_rows = pair_rows(ring, me, owner, shape->lk), take_rows = pair_rows(ring, giver, me, shape->lk);
+    auto whole = [&](const RowRuns& rr) { return rr.n == 1 && rr.lo[0] == 0 && rr.hi[0] == shape->lk; };
     if (compute) {
       use_staged(msg, ring->stage[slot], &p.k, &p.v, &p.mod);
       if ((rc = wait_kv(ring, t, s))) return rc;
@@ -1253,26 +1374,70 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
         // the owner's rpart[slot] is free once it has summed the contribution of step t-2
         const uint64_t need = t >= 3 ? ring->epoch + t - 1 : ring->epoch;
         if ((rc = launch_wait(ring, ring->push_stream, kFlagAdded + owner, need))) return rc;
-        if ((rc = push_mark(ring, ring->push_stream, (double)(dk_b + dv_b)))) return rc;
-        RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
-                                cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
         if ((rc = push_mark(ring, ring->push_stream, 0))) return rc;
+        double sent = 0;
+        if (whole(give_rows)) {
+          RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
+                                  cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
+          sent = (double)(dk_b + dv_b);
+        } else {  // only the key rows this rank's queries saw: one strided copy per run, dK and dV
+          for (int k = 0; k < give_rows.n; ++k)
+            for (int which = 0; which < 2; ++which) {
+              const size_t d = which ? shape->dv : shape->dk, base = which ? dk_b : 0;
+              const size_t pitch = (size_t)shape->lk * d * 4, off = base + (size_t)give_rows.lo[k] * d * 4;
+              const size_t width = (size_t)(give_rows.hi[k] - give_rows.lo[k]) * d * 4;
+              RA_CUDA(cudaMemcpy2DAsync((char*)ring->peers[owner].rpart[slot] + off, pitch, (char*)ring->part[slot].ptr + off, pitch,
+                                        width, (size_t)shape->b * shape->h, cudaMemcpyDeviceToDevice, ring->push_stream),
+                      "cudaMemcpy2DAsync(peer dK/dV rows)");
+              sent += (double)width * shape->b * shape->h;
+            }
+        }
+        if ((rc = push_mark(ring, ring->push_stream, sent))) return rc;
         if ((rc = launch_set(ring, ring->push_stream, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
         RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
       }
       // owner side, on the reduce stream
       if (receive && (rc = launch_wait(ring, ring->reduce_stream, kFlagPartReady + slot, ring->epoch + t))) return rc;
     } else if (compute || receive) {
+      // whole buffers, or one message per (batch, head) and row run of dK and of dV
+      auto nccl_rows = [&](char* base, const RowRuns& rr, int peer, bool send) -> int {
+        auto one = [&](char* ptr, size_t n) -> int {
+          if (send) RA_NCCL(api->Send(ptr, n, ncclChar, peer, ring->comm, ring->push_stream), "ncclSend");
+          else RA_NCCL(api->Recv(ptr, n, ncclChar, peer, ring->comm, ring->push_stream), "ncclRecv");
+          return 0;
+        };
+        if (whole(rr)) return one(base, dk_b + dv_b);
+        int rc2;
+        for (int which = 0; which < 2; ++which) {
+          const size_t d = which ? shape->dv : shape->dk, off0 = which ? dk_b : 0;
+          for (int64_t seg = 0; seg < (int64_t)shape->b * shape->h; ++seg)
+            for (int k = 0; k < rr.n; ++k)
+              if ((rc2 = one(base + off0 + ((size_t)seg * shape->lk + rr.lo[k]) * d * 4, (size_t)(rr.hi[k] - rr.lo[k]) * d * 4))) return rc2;
+        }
+        return 0;
+      };
       RA_NCCL(api->GroupStart(), "ncclGroupStart");
-      if (compute) RA_NCCL(api->Send(ring->part[slot].ptr, dk_b + dv_b, ncclChar, owner, ring->comm, ring->push_stream), "ncclSend");
-      if (receive) RA_NCCL(api->Recv(ring->rpart[slot], dk_b + dv_b, ncclChar, giver, ring->comm, ring->push_stream), "ncclRecv");
+      if (compute && (rc = nccl_rows((char*)ring->part[slot].ptr, give_rows, owner, true))) return rc;
+      if (receive && (rc = nccl_rows((char*)ring->rpart[slot], take_rows, giver, false))) return rc;
       RA_NCCL(api->GroupEnd(), "ncclGroupEnd");
       RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
     }
     if (receive) {
       // NCCL transport: the sum runs on the transfer stream, which has not seen the own block yet
       if (!ring->p2p) RA_CUDA(cudaStreamWaitEvent(add_stream, ring->ev_step0, 0), "cudaStreamWaitEvent");
-      e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot], (int64_t)((dk_b + dv_b) / 4), add_stream);
+      if (whole(take_rows)) {
+        e = launch_add_f32(dk_acc, (const float*)ring->rpart[slot], (int64_t)((dk_b + dv_b) / 4), add_stream);
+      } else {
+        e = cudaSuccess;
+        for (int k = 0; k < take_rows.n && e == cudaSuccess; ++k)
+          for (int which = 0; which < 2 && e == cudaSuccess; ++which) {
+            const int64_t d = which ? shape->dv : shape->dk;
+            float* dst = which ? dv_acc : dk_acc;
+            const float* src = (const float*)((const char*)ring->rpart[slot] + (which ? dk_b : 0));
+            e = launch_add_rows_f32(dst + take_rows.lo[k] * d, src + take_rows.lo[k] * d, (int64_t)shape->b * shape->h,
+                                    (int64_t)(take_rows.hi[k] - take_rows.lo[k]) * d, (int64_t)shape->lk * d, add_stream);
+          }
+      }
       if (e != cudaSuccess) return fail_cuda(e, "add");
     }
     // published even when nothing was received: it is what frees rpart[slot] for the step after next
@@ -1333,7 +1498,7 @@ int ra_ring_reserve(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod
   const KvMessage msg = make_kv_message(shape, none, none, m);
   RA_CUDA(ring->state.reserve(z.o_bytes + 2 * z.ml_bytes), "cudaMalloc(state)");
   if (backward) {
-    RA_CUDA(ring->grads.reserve(z.delta_b + z.dq_b + z.dk_b + z.dv_b + z.own2_dk_b + z.own2_dv_b), "cudaMalloc(grads)");
+    RA_CUDA(ring->grads.reserve(3 * z.delta_b + z.dq_b + z.dk_b + z.dv_b + z.own2_dk_b + z.own2_dv_b), "cudaMalloc(grads)");
     if (N > 1)
       for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(z.dk_b + z.dv_b), "cudaMalloc(part)");
   }
@@ -1370,8 +1535,8 @@ int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score
   const int b = shape->b, nq = (shape->lq + 127) / 128, nk = (shape->lk + 127) / 128;
   const size_t per_rank = (size_t)b * (nq + nk);
   TileMeta *mine = nullptr, *all = nullptr;
-  int* need_dev = nullptr;
-  std::vector<int> need_host((size_t)N * N, 1);
+  int* need_dev = nullptr;  // [N * N] need flags, then [N * N * 4] row runs
+  std::vector<int> need_host((size_t)N * N * 5, 1);
   auto cleanup = [&]() {
     if (mine) cudaFree(mine);
     if (all) cudaFree(all);
@@ -1385,7 +1550,7 @@ int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score
   cudaError_t e;
   if ((e = cudaMalloc((void**)&mine, per_rank * sizeof(TileMeta))) != cudaSuccess ||
       (e = cudaMalloc((void**)&all, per_rank * sizeof(TileMeta) * N)) != cudaSuccess ||
-      (e = cudaMalloc((void**)&need_dev, sizeof(int) * N * N)) != cudaSuccess)
+      (e = cudaMalloc((void**)&need_dev, sizeof(int) * N * N * 5)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaMalloc(plan)"));
   plan_meta_kernel<<<dim3((nq + 7) / 8, b), 256, 0, s>>>(mine, m.q_pos, m.q_seg, m.q_pre, shape->lq, nq);
   plan_meta_kernel<<<dim3((nk + 7) / 8, b), 256, 0, s>>>(mine + (size_t)b * nq, m.kv_pos, m.kv_seg, m.kv_pre, shape->lk, nk);
@@ -1398,19 +1563,21 @@ int ra_ring_plan_create(ra_ring_t* ring, const ra_shape_t* shape, const ra_score
   NcclApi* api = nccl_api();
   ncclResult_t nr = api->AllGather(mine, all, per_rank * sizeof(TileMeta), ncclChar, ring->comm, s);
   if (nr != ncclSuccess) return bail(fail_nccl(nr, "ncclAllGather(plan)"));
-  if ((e = cudaMemsetAsync(need_dev, 0, sizeof(int) * N * N, s)) != cudaSuccess) return bail(fail_cuda(e, "cudaMemsetAsync"));
-  plan_need_kernel<<<N * N, 256, 0, s>>>(all, N, b, nq, nk, m.kinds, m.window, need_dev);
+  if ((e = cudaMemsetAsync(need_dev, 0, sizeof(int) * N * N * 5, s)) != cudaSuccess) return bail(fail_cuda(e, "cudaMemsetAsync"));
+  plan_need_kernel<<<N * N, 256, 0, s>>>(all, N, b, nq, nk, m.kinds, m.window, need_dev, need_dev + N * N);
   count_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return bail(fail_cuda(e, "plan_need_kernel"));
-  if ((e = cudaMemcpyAsync(need_host.data(), need_dev, sizeof(int) * N * N, cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+  if ((e = cudaMemcpyAsync(need_host.data(), need_dev, sizeof(int) * N * N * 5, cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
       (e = cudaStreamSynchronize(s)) != cudaSuccess)
     return bail(fail_cuda(e, "plan readback"));
   // later NCCL traffic on the push stream comes after the all-gather
   if ((e = cudaEventRecord(ring->ev_start, s)) != cudaSuccess ||
       (e = cudaStreamWaitEvent(ring->push_stream, ring->ev_start, 0)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaStreamWaitEvent"));
-  for (size_t i = 0; i < need_host.size(); ++i) plan->need[i] = need_host[i] ? 1 : 0;
+  for (size_t i = 0; i < (size_t)N * N; ++i) plan->need[i] = need_host[i] ? 1 : 0;
   for (int r = 0; r < N; ++r) plan->need[(size_t)r * N + r] = 1;  // the own block always runs
+  plan->lk = shape->lk;
+  plan->rows.assign(need_host.begin() + (size_t)N * N, need_host.end());
   cleanup();
   *out = plan;
   return 0;
@@ -1422,6 +1589,22 @@ int ra_ring_plan_need(const ra_ring_plan_t* plan, int32_t q_rank, int32_t kv_ran
   if (!plan) return fail(-6, "plan is NULL");
   if (q_rank < 0 || kv_rank < 0 || q_rank >= plan->nranks || kv_rank >= plan->nranks) return fail(-33, "bad rank");
   return plan->need[(size_t)q_rank * plan->nranks + kv_rank];
+}
+
+int ra_ring_plan_rows(const ra_ring_plan_t* plan, int32_t q_rank, int32_t kv_rank, int32_t runs[4]) {
+  if (!plan || !runs) return fail(-6, "plan or result pointer is NULL");
+  if (q_rank < 0 || kv_rank < 0 || q_rank >= plan->nranks || kv_rank >= plan->nranks) return fail(-33, "bad rank");
+  const int chunks = (plan->lk + 127) / 128;
+  if (plan->rows.empty()) {  // no mask to summarise: the whole block
+    runs[0] = 0, runs[1] = plan->lk, runs[2] = runs[3] = 0;
+    return 0;
+  }
+  for (int i = 0; i < 4; ++i) {
+    const int v = plan->rows[((size_t)q_rank * plan->nranks + kv_rank) * 4 + i] * 128;
+    runs[i] = v > plan->lk ? plan->lk : v;
+  }
+  (void)chunks;
+  return 0;
 }
 
 int ra_ring_use_plan(ra_ring_t* ring, const ra_ring_plan_t* plan) {

@@ -622,6 +622,50 @@ cudaError_t launch_strict_nan(int b, int h, int lq, int lk, int dk_dim, int dv_d
   return cudaGetLastError();
 }
 
+__global__ void bwd_row_terms_kernel(const float* __restrict__ lse, const float* __restrict__ delta, float scale,
+                                     int clamp, int64_t n, float* __restrict__ nl2, float* __restrict__ nds) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float x = -lse[i] * 1.4426950408889634f;
+  nl2[i] = clamp ? fminf(x, 1e30f) : x;
+  nds[i] = -delta[i] * scale;
+}
+
+__global__ void add_rows_f32_kernel(float* __restrict__ dst, const float* __restrict__ src, int64_t seg_elems,
+                                    int64_t pitch) {
+  float* d = dst + (int64_t)blockIdx.y * pitch;
+  const float* c = src + (int64_t)blockIdx.y * pitch;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i + 3 < seg_elems; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 a = *reinterpret_cast<float4*>(d + i);
+    const float4 x = *reinterpret_cast<const float4*>(c + i);
+    a.x += x.x, a.y += x.y, a.z += x.z, a.w += x.w;
+    *reinterpret_cast<float4*>(d + i) = a;
+  }
+}
+
+cudaError_t launch_bwd_row_terms(const float* lse, const float* delta, float scale, int clamp, int64_t n, float* nl2,
+                                 float* nds, cudaStream_t s) {
+  bwd_row_terms_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(lse, delta, scale, clamp, n, nl2, nds);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add_rows_f32(float* dst, const float* src, int64_t nseg, int64_t seg_elems, int64_t pitch, cudaStream_t s) {
+  if (nseg <= 0 || seg_elems <= 0) return cudaSuccess;
+  if (seg_elems % 4 || pitch % 4 || nseg > 65535) {  // odd sizes: one flat add per segment
+    for (int64_t g = 0; g < nseg; ++g) {
+      cudaError_t e = launch_add_f32(dst + g * pitch, src + g * pitch, seg_elems, s);
+      if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+  }
+  int64_t want = (seg_elems / 4 + 255) / 256;
+  dim3 grid((unsigned)(want > 64 ? 64 : want), (unsigned)nseg);
+  add_rows_f32_kernel<<<grid, 256, 0, s>>>(dst, src, seg_elems, pitch);
+  count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_add_f32(float* dst, const float* src, int64_t n, cudaStream_t s) {
   int64_t want = (n / 4 + 255) / 256;
   int grid = (int)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));

@@ -387,6 +387,13 @@ class RingPlan:
         n = self.ring.size
         return [[self.needed(r, o) for o in range(n)] for r in range(n)]
 
+    def rows(self, q_rank: int, kv_rank: int):
+        """Runs [(first, end), ...] of K/V rows of `kv_rank`'s block that travel to `q_rank` (and
+        whose dK/dV come back): at most one per half of the block."""
+        runs = (C.c_int32 * 4)()
+        check(lib.ra_ring_plan_rows(self.handle, q_rank, kv_rank, runs))
+        return [(runs[i], runs[i + 1]) for i in (0, 2) if runs[i] < runs[i + 1]]
+
     def __del__(self):
         if getattr(self, "handle", None):
             lib.ra_ring_plan_destroy(self.handle)

@@ -79,6 +79,22 @@ def _worker(rank, world, port, case, q_out):
                         assert got[r][o] or not want[r][o], f"plan drops pair ({r}, {o}) that has visible pairs"
                 if not all(map(all, want)):
                     assert sum(map(sum, got)) < world * world, "the plan keeps every pair although some are empty"
+                # row runs: every key row some query of r sees lies inside a run of the pair (r, o); a
+                # window mask needs less than the whole block of its left neighbour
+                moved = 0
+                for r in range(world):
+                    for o in range(world):
+                        if r == o or not got[r][o]:
+                            continue
+                        runs = plan.rows(r, o)
+                        inside = np.zeros(ck, bool)
+                        for lo, hi in runs:
+                            inside[lo:hi] = True
+                        seen = vis[np.ix_(shard_of(r)[0], shard_of(o)[1])].any(axis=0)
+                        assert not (seen & ~inside).any(), f"pair ({r}, {o}): visible key rows outside the runs {runs}"
+                        moved += int(inside.sum())
+                if window and window < ck // 2:
+                    assert moved < ck * sum(got[r][o] for r in range(world) for o in range(world) if r != o), "no halo"
             for rep in range(2):  # second pass reuses the ring's buffers
                 tq.grad = tk.grad = tv.grad = None
                 out = ra.ring_attention(tq, tk, tv, "sp", bias_fn=fn, bias_q_kwargs=qkw, bias_kv_kwargs=kkw,
