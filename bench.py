@@ -40,6 +40,8 @@ WORKLOADS = {
     "documents_128k": dict(dtype="bf16", b=1, h=32, d=128, s=131072, mask="documents"),
     # ALiBi slopes 2^(-8(h+1)/16), visible iff 0 <= q_pos - kv_pos < 4096; forward only
     "alibi_window_64k": dict(dtype="bf16", b=4, h=16, d=64, s=65536, mask="alibi+window", window=4096, backward=False),
+    # the same mask on a quarter of the length: the ncu capture case of the head-dim-64 forward
+    "alibi_window_16k": dict(dtype="bf16", b=4, h=16, d=64, s=16384, mask="alibi+window", window=4096, backward=False),
     # 131072 tokens per GPU (1 Mi tokens at 8 GPUs), inputs ~ N(0, 0.5^2)
     "causal_1m": dict(dtype="bf16", b=1, h=8, d=128, s_per_gpu=131072, mask="causal", std=0.5),
 }

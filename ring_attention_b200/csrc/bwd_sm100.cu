@@ -127,18 +127,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     fence_barrier_init();
     fence_proxy_async_smem();
   }
-  if (warp == 9) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
-  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
-                 tmem_dK = tmem_base + 256 + D;
-  const bool bad = *abort_flag != 0;
-
   TileMeta mk;
   if (masked) mk = P.meta_kv[bb * P.n_kv_tiles + kt];
   // First query tile >= i that has a pair visible to this CTA's K/V tile (n_q_tiles if there is
@@ -180,6 +168,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     return P.n_q_tiles;
   };
 
+  // Every warp looks up the CTA's first visible query tile.  A K/V tile that no query of this
+  // block sees (the tiles past the diagonal of a causal pair of shards) takes no tensor memory.
+  Window win0;
+  const int first_tile = next_active(win0, 0) & kTileIdx;
+  const bool has_work = first_tile < P.n_q_tiles;
+  if (warp == 9 && has_work) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = has_work ? __shfl_sync(0xffffffffu, *tmem_slot, 0) : 0u;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256,
+                 tmem_dK = tmem_base + 256 + D;
+  const bool bad = *abort_flag != 0;
+
   if (bad) {
     // fall through to the common exit
   } else if (warp == 8) {
@@ -192,8 +197,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       prefetch_tensormap(&P.map_do);
       if constexpr (D == 128) prefetch_tensormap(&P.map_dq);
     }
-    Window wq, wdo;
-    const int i = next_active(wq, 0) & kTileIdx;
+    Window wq = win0, wdo = win0;
+    const int i = first_tile;
     if (i < P.n_q_tiles && lane == 0) {
       mbar_arrive_expect_tx(&bars[KV_FULL], 2 * TILE_BYTES);
       for (int pn = 0; pn < PANELS; ++pn) {
@@ -304,8 +309,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       // so that the compute warps form P(n+1) under dQ(n)/dK(n), drain dQ(n) under dK(n), and
       // form dS(n+1) under dV(n+1)/S(n+2).
       bool ok = true;
-      Window win;
-      int i = next_active(win, 0) & kTileIdx;
+      Window& win = win0;
+      int i = first_tile;
       if (i < P.n_q_tiles) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars[KV_FULL], 0, abort_flag, P.status, kStBwdMma) &&
                                          mbar_wait(&bars[Q_FULL0], 0, abort_flag, P.status, kStBwdMma) &&
@@ -390,11 +395,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
     uint32_t sv[2][32];
     const float alibi_over_scale = alibi ? p.mod.slopes[hh] / p.scale : 0.f;
     const float slope2 = alibi ? p.mod.slopes[hh] * kLog2e : 0.f;
-    Window win;
+    Window& win = win0;
 
     // One loop body serves every tile so that each phase exists once in the instruction
     // stream: step k does dS^T(k-1), then P^T(k), then the dQ drain of tile k-1.
-    int i_prev = -1, e_cur = next_active(win, 0), i_cur = e_cur & kTileIdx;
+    int i_prev = -1, e_cur = next_active(win, first_tile), i_cur = e_cur & kTileIdx;
     int32_t q0_cur = win.hit_pos0;  // first query position of the tile (used when its positions are contiguous)
     for (int k = 0; ok; ++k) {
       const bool have_prev = k > 0, have_cur = i_cur < P.n_q_tiles;
@@ -505,10 +510,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
             }
           }
         }
-        uint32_t pk[32];
+        // P^T of warpgroup g: 32 packed columns at S column 64g, stored in two halves (fewer live registers)
 #pragma unroll
-        for (int e = 0; e < 32; ++e) pk[e] = pack_bf16(pf[2 * e], pf[2 * e + 1]);
-        tmem_st32(tmem_S + lane_off + g * 64, pk);  // P^T of warpgroup g: 32 packed columns at S column 64g
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pf[32 * hf + 2 * e], pf[32 * hf + 2 * e + 1]);
+          tmem_st16(tmem_S + lane_off + g * 64 + 16 * hf, pk);
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bars[P_READY]);
@@ -659,7 +668,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 9 && has_work) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
