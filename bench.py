@@ -366,6 +366,8 @@ def main():
                     help="token->rank layout at N>1: zigzag balances causal work, contiguous is the reference tests' layout")
     ap.add_argument("--plan", action="store_true",
                     help="at N>1: leave out the ring steps whose block the mask empties (made once, before the warm-up)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="rank 0 prints, on stderr, when each block launch and each wait for a transfer of the last timed step ran")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -487,6 +489,13 @@ def main():
     bwd_blocks = ring.last_block_ms(True) if backward else (0.0, 1)
     exposed_ms = [ring.last_timing(False)[1] + (ring.last_timing(True)[1] if backward else 0.0)]
     launches = lib.ra_launch_count() - launches0
+    if args.timeline and rank == 0:
+        for name, back in (("forward", False),) + ((("backward", True),) if backward else ()):
+            blocks_tl, waits_tl = ring.last_timeline(back)
+            tot = ring.last_timing(back)[0]
+            print(f"timeline of the last {name} call ({tot:.3f} ms): block launches "
+                  + " ".join(f"[{a:.3f},{b_:.3f}]" for a, b_ in blocks_tl) + " | waits for transfers "
+                  + " ".join(f"[{a:.3f},{b_:.3f}]" for a, b_ in waits_tl), file=sys.stderr, flush=True)
     step_ms = e_begin.elapsed_time(e_end) / args.steps - flush_ms
     t = torch.tensor([step_ms], device="cuda")
     if world > 1:
@@ -696,7 +705,12 @@ def main():
                 "launches_per_step": int(bwd_blocks[1] if backward else fwd_blocks[1]),
                 "fwd_block": {"launch_ms": fwd_ms, "achieved": fwd_flops_launch / (fwd_ms * 1e-3) / 1e12},
             },
-            "exposed_comm_ms": max(exposed_all), "exposed_comm_frac": max(exposed_all) / step_ms,
+            # Per rank: time a compute lane waited for a transfer while no block kernel of that rank ran.
+            # A rank also waits when a peer is simply slower (the GPUs of a box differ by several per
+            # cent at the power cap): the rank that waited least is the one that set the pace, and its
+            # figure is what the transfers themselves cost; the largest figure is printed beside it.
+            "exposed_comm_ms": min(exposed_all), "exposed_comm_frac": min(exposed_all) / step_ms,
+            "exposed_comm_ms_max_over_ranks": max(exposed_all),
             "exposed_comm_ms_per_rank": exposed_all,
             "gpu_launches": int(launches),
             "parity": {"ok": all(x["ok"] for x in parity_all), "max_excess": max(x["max_excess"] for x in parity_all),

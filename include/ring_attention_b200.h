@@ -202,7 +202,7 @@ int ra_ring_transport(const ra_ring_t* ring);
 
 /* Allocates, ahead of time, everything ra_ring_fwd (and, with backward != 0, ra_ring_bwd)
  * keeps in the handle for calls of this shape: the fp32 carried state (ring.py:124-126), the
- * gradient accumulators (ring.py:198-200), the double buffers that receive the other ranks'
+ * gradient accumulators (ring.py:198-200), the staging slots that receive the other ranks'
  * K/V blocks (the operands of ring.py:120) and dK/dV contributions, and, with the peer-copy
  * transport, the exchange and mapping of their IPC handles.  This is the only place where the
  * ring calls cudaMalloc and synchronises the device: after it, ring calls of the same or a
@@ -235,7 +235,7 @@ int ra_ring_source(int32_t rank, int32_t nranks, int32_t step);
 /* Fused ring forward: _ring_attention_fwd (ring.py:79-137).  q,k,v are this rank's
  * shards; out gets this rank's rows in shape->dtype, lse gets L (fp32 [b,h,lq]).
  * K/V (and the kv-side arrays of mod) of the other ranks are fetched over NVLink on a
- * side stream into double buffers while the current block is computed.
+ * side stream into a ring of staging slots while earlier blocks are computed.
  * Every rank of the ring must make the same call with the same shape.
  */
 int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
@@ -300,6 +300,11 @@ int ra_ring_last_timing(ra_ring_t* ring, int32_t backward, float* total_ms, floa
  * there were.  Timing must be on; the two directions are kept
  * apart so that a forward + backward step can be queried once, after it ended. */
 int ra_ring_last_block_ms(ra_ring_t* ring, int32_t backward, float* block_ms, int32_t* launches);
+/* The same call as a timeline: [begin, end] in ms from the call's start of every block launch
+ * (in launch order; launches of the two compute lanes overlap) and of every wait for a transfer,
+ * at most max_items of each (blocks and waits hold 2 * max_items floats).  Timing must be on. */
+int ra_ring_last_timeline(ra_ring_t* ring, int32_t backward, int32_t max_items, float* blocks, int32_t* n_blocks,
+                          float* waits, int32_t* n_waits);
 /* Peer-copy transport: bytes this rank pushed to other ranks (K/V blocks, and dK/dV
  * contributions in the backward: the traffic of ring.py:120 and :195) during the last forward /
  * backward ring call, and the device time of those copies on the transfer stream, event to

@@ -87,6 +87,8 @@ _SIGNATURES = {
     "ra_ring_last_timing": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_float), _P(C.c_float)]),
     "ra_ring_last_block_ms": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_float), _P(C.c_int32)]),
     "ra_ring_last_push": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_double), _P(C.c_float)]),
+    "ra_ring_last_timeline": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, _P(C.c_float), _P(C.c_int32), _P(C.c_float),
+                                        _P(C.c_int32)]),
 }
 
 EXPORTS = tuple(_SIGNATURES)

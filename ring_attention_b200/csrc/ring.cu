@@ -153,7 +153,12 @@ namespace ringimpl {
 // head of the next; a step's staging slot, contribution buffer, forward state and PROGRESS
 // counter are those of its lane (slot = lane = step parity), and steps of one lane stay ordered.
 constexpr int kMaxRanks = 64;
-constexpr int kFlagKvReady = 0, kFlagPartReady = 2, kFlagProgress = 8, kFlagAdded = 8 + 2 * kMaxRanks;
+// Staging slots for incoming K/V blocks, buffers for outgoing and for incoming dK/dV
+// contributions: slot = step % kSlots.  Two would do for one compute lane; with two lanes the
+// blocks of steps t and t+1 are both in use while the block of step t+2 should already be
+// travelling, and a contribution buffer must not wait for its predecessor's transfer.
+constexpr int kSlots = 4;
+constexpr int kFlagKvReady = 0, kFlagPartReady = 4, kFlagProgress = 8, kFlagAdded = 8 + 2 * kMaxRanks;
 constexpr int kNumFlags = 8 + 3 * kMaxRanks;
 constexpr int progress_flag(int lane, int rank) { return kFlagProgress + lane * kMaxRanks + rank; }
 constexpr uint32_t kStRingWait = 1u << 16;  // status bit: a cross-GPU wait ran out
@@ -198,7 +203,7 @@ __global__ void set_flags_kernel(FlagList list, uint64_t value, const unsigned i
 }
 
 struct IpcBundle {
-  cudaIpcMemHandle_t stage[2], rpart[2], flags;
+  cudaIpcMemHandle_t stage[kSlots], rpart[kSlots], flags;
 };
 
 }  // namespace ringimpl
@@ -223,14 +228,19 @@ struct ra_ring {
   cudaStream_t push_stream = nullptr;    // transfers this rank issues (high priority)
   cudaStream_t reduce_stream = nullptr;  // sums of dK/dV contributions this rank receives (p2p)
   cudaStream_t lane_stream = nullptr;    // second compute lane: the odd block steps
+  // dK/dV contributions this rank gives (p2p): a stream of their own, so that the K/V block of a
+  // later step never queues behind a contribution that waits for its block kernel.  With the
+  // NCCL transport it is the transfer stream itself (one communicator, one stream).
+  cudaStream_t give_stream = nullptr;
+  cudaEvent_t ev_give_tail = nullptr;
   cudaEvent_t ev_lane_start = nullptr, ev_lane_done = nullptr;
-  cudaEvent_t ev_start = nullptr, ev_recv[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
-  cudaEvent_t ev_part[2] = {nullptr, nullptr}, ev_sent[2] = {nullptr, nullptr}, ev_tail = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_recv[ringimpl::kSlots] = {}, ev_done[ringimpl::kSlots] = {};
+  cudaEvent_t ev_part[ringimpl::kSlots] = {}, ev_sent[ringimpl::kSlots] = {}, ev_tail = nullptr;
   cudaEvent_t ev_push_tail = nullptr, ev_step0 = nullptr;
   bool p2p = false;
   // buffers other ranks write into (cudaMalloc'ed, exported through CUDA IPC under p2p)
-  void* stage[2] = {nullptr, nullptr};  // K, V and the kv-side score-mod arrays of a remote block
-  void* rpart[2] = {nullptr, nullptr};  // a remote rank's dK/dV contribution for this rank's block
+  void* stage[ringimpl::kSlots] = {};  // K, V and the kv-side score-mod arrays of a remote block
+  void* rpart[ringimpl::kSlots] = {};  // a remote rank's dK/dV contribution for this rank's block
   size_t stage_bytes = 0, rpart_bytes = 0;
   uint64_t* flags = nullptr;
   // [0] abort word: set by a wait that ran out, checked by every later wait and flag store of
@@ -238,8 +248,8 @@ struct ra_ring {
   unsigned int* guard = nullptr;
   long long wait_cycles = 0;  // bound of one wait for a peer, in SM cycles
   struct Peer {
-    void* stage[2] = {nullptr, nullptr};
-    void* rpart[2] = {nullptr, nullptr};
+    void* stage[ringimpl::kSlots] = {};
+    void* rpart[ringimpl::kSlots] = {};
     uint64_t* flags = nullptr;
   };
   std::vector<Peer> peers;  // this process's view of every rank's buffers ([rank] = own pointers)
@@ -248,7 +258,7 @@ struct ra_ring {
   uint64_t epoch = 0;  // global step id of the next call's step 0 (advances by nranks per call)
   Buffer state;    // o (fp32), m, l
   Buffer grads;    // delta, dq, dk, dv accumulators (fp32)
-  Buffer part[2];  // this rank's dK/dV contribution for a remote block
+  Buffer part[ringimpl::kSlots];  // this rank's dK/dV contributions for remote blocks
   bool timing = false;
   // timing, kept per direction ([0] forward call, [1] backward call)
   std::vector<cudaEvent_t> t_events[2];  // pairs bracketing each wait on a transfer
@@ -502,7 +512,7 @@ void close_peers(ra_ring_t* r) {
   for (int j = 0; j < (int)r->peers.size(); ++j) {
     if (j == r->rank) continue;
     ra_ring::Peer& p = r->peers[j];
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kSlots; ++i) {
       if (p.stage[i]) cudaIpcCloseMemHandle(p.stage[i]);
       if (p.rpart[i]) cudaIpcCloseMemHandle(p.rpart[i]);
       p.stage[i] = p.rpart[i] = nullptr;
@@ -567,7 +577,7 @@ int exchange_handles(ra_ring_t* r) {
   IpcBundle mine;
   memset(&mine, 0, sizeof(mine));
   int ok_local = 1;
-  for (int i = 0; i < 2 && ok_local; ++i)
+  for (int i = 0; i < kSlots && ok_local; ++i)
     if (cudaIpcGetMemHandle(&mine.stage[i], r->stage[i]) != cudaSuccess ||
         cudaIpcGetMemHandle(&mine.rpart[i], r->rpart[i]) != cudaSuccess)
       ok_local = 0;
@@ -585,7 +595,7 @@ int exchange_handles(ra_ring_t* r) {
   for (int j = 0; j < r->nranks; ++j) {
     ra_ring::Peer& p = r->peers[j];
     if (j == r->rank) {
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < kSlots; ++i) {
         p.stage[i] = r->stage[i];
         p.rpart[i] = r->rpart[i];
       }
@@ -593,7 +603,7 @@ int exchange_handles(ra_ring_t* r) {
       continue;
     }
     if (!ok_local) continue;
-    for (int i = 0; i < 2 && ok_local; ++i)
+    for (int i = 0; i < kSlots && ok_local; ++i)
       if (cudaIpcOpenMemHandle(&p.stage[i], all[j].stage[i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
           cudaIpcOpenMemHandle(&p.rpart[i], all[j].rpart[i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
         ok_local = 0;
@@ -626,7 +636,7 @@ int ensure_shared(ra_ring_t* r, size_t stage_need, size_t rpart_need) {
   if (r->p2p) close_peers(r);
   const size_t ns = stage_need > r->stage_bytes ? stage_need : r->stage_bytes;
   const size_t np = rpart_need > r->rpart_bytes ? rpart_need : r->rpart_bytes;
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < kSlots; ++i) {
     if (r->stage[i]) cudaFree(r->stage[i]);
     if (r->rpart[i]) cudaFree(r->rpart[i]);
     r->stage[i] = r->rpart[i] = nullptr;
@@ -725,15 +735,15 @@ int push_part(ra_ring_t* r, const KvMessage& msg, int i, void* dst_base, const R
 }
 
 int send_kv(ra_ring_t* r, const KvMessage& msg, int t, int lk) {
-  const int N = r->nranks, me = r->rank, slot = t & 1;
+  const int N = r->nranks, me = r->rank, slot = t % kSlots;
   const int to = (me + t) % N, from = ((me - t) % N + N) % N;
   const bool do_send = pair_needed(r, to, me), do_recv = pair_needed(r, me, from);
   if (r->p2p) {
     if (!do_send) return 0;
-    // the consumer's stage[slot] was last read by its step t-2 (or by its previous call)
-    const uint64_t need = t >= 3 ? r->epoch + t - 1 : r->epoch;
+    // the consumer's stage[slot] was last read by its step t - kSlots, on the same lane (or by its previous call)
+    const uint64_t need = t > kSlots ? r->epoch + t - kSlots + 1 : r->epoch;
     int rc;
-    if ((rc = launch_wait(r, r->push_stream, progress_flag(slot, to), need))) return rc;
+    if ((rc = launch_wait(r, r->push_stream, progress_flag(t & 1, to), need))) return rc;
     double sent = 0;
     const RowRuns rr = pair_rows(r, to, me, lk);  // what the consumer's queries see of this rank's block
     if ((rc = push_mark(r, r->push_stream, 0))) return rc;
@@ -742,7 +752,7 @@ int send_kv(ra_ring_t* r, const KvMessage& msg, int t, int lk) {
     if ((rc = push_mark(r, r->push_stream, sent))) return rc;
     return launch_set(r, r->push_stream, to, kFlagKvReady + slot, r->epoch + t);
   }
-  if (t >= 2) RA_CUDA(cudaStreamWaitEvent(r->push_stream, r->ev_done[slot], 0), "cudaStreamWaitEvent");
+  if (t > kSlots) RA_CUDA(cudaStreamWaitEvent(r->push_stream, r->ev_done[slot], 0), "cudaStreamWaitEvent");
   int rc;
   if ((do_send || do_recv) && (rc = exchange_kv_nccl(r, msg, r->stage[slot], do_send ? to : -1, do_recv ? from : -1, lk))) return rc;
   RA_CUDA(cudaEventRecord(r->ev_recv[slot], r->push_stream), "cudaEventRecord");
@@ -751,10 +761,10 @@ int send_kv(ra_ring_t* r, const KvMessage& msg, int t, int lk) {
 
 // Make the compute stream wait until the block of step t (t >= 1) has landed in stage[t & 1].
 int wait_kv(ra_ring_t* r, int t, cudaStream_t stream) {
-  if (!r->p2p) return wait_transfer(r, stream, r->ev_recv[t & 1]);
+  if (!r->p2p) return wait_transfer(r, stream, r->ev_recv[t % kSlots]);
   int rc;
   if ((rc = timing_mark(r, stream))) return rc;
-  if ((rc = launch_wait(r, stream, kFlagKvReady + (t & 1), r->epoch + t))) return rc;
+  if ((rc = launch_wait(r, stream, kFlagKvReady + t % kSlots, r->epoch + t))) return rc;
   return timing_mark(r, stream);
 }
 
@@ -762,7 +772,7 @@ int wait_kv(ra_ring_t* r, int t, cudaStream_t stream) {
 int step_done(ra_ring_t* r, int t, cudaStream_t stream) {
   if (r->nranks == 1) return 0;
   if (r->p2p) return launch_set(r, stream, -1, progress_flag(t & 1, r->rank), r->epoch + t + 1);
-  RA_CUDA(cudaEventRecord(r->ev_done[t & 1], stream), "cudaEventRecord");
+  RA_CUDA(cudaEventRecord(r->ev_done[t % kSlots], stream), "cudaEventRecord");
   return 0;
 }
 
@@ -773,6 +783,7 @@ int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
     RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
     if (ring->reduce_stream) RA_CUDA(cudaStreamWaitEvent(ring->reduce_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
     RA_CUDA(cudaStreamWaitEvent(ring->lane_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
+    RA_CUDA(cudaStreamWaitEvent(ring->give_stream, ring->ev_start, 0), "cudaStreamWaitEvent");
   }
   ring->dir = dir;
   ring->t_used[dir] = 0;
@@ -802,6 +813,8 @@ int end_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
     // the pushes read the caller's tensors: they must be over before the caller may reuse them
     RA_CUDA(cudaEventRecord(ring->ev_push_tail, ring->push_stream), "cudaEventRecord");
     RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_push_tail, 0), "cudaStreamWaitEvent");
+    RA_CUDA(cudaEventRecord(ring->ev_give_tail, ring->give_stream), "cudaEventRecord");
+    RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_give_tail, 0), "cudaStreamWaitEvent");
     ring->epoch += ring->nranks;
   }
   if (ring->timing) RA_CUDA(cudaEventRecord(ring->t_end[dir], stream), "cudaEventRecord");
@@ -867,11 +880,17 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
     return bail(fail_cuda(e, "cudaDeviceGetStreamPriorityRange"));
   if ((e = cudaStreamCreateWithPriority(&r->push_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
       (e = cudaStreamCreateWithPriority(&r->reduce_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
-      (e = cudaStreamCreateWithPriority(&r->lane_stream, cudaStreamNonBlocking, prio_low)) != cudaSuccess)
+      (e = cudaStreamCreateWithPriority(&r->lane_stream, cudaStreamNonBlocking, prio_low)) != cudaSuccess ||
+      (e = cudaStreamCreateWithPriority(&r->give_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaStreamCreate"));
-  cudaEvent_t* evs[] = {&r->ev_start, &r->ev_recv[0], &r->ev_recv[1], &r->ev_done[0], &r->ev_done[1],
-                        &r->ev_part[0], &r->ev_part[1], &r->ev_sent[0], &r->ev_sent[1], &r->ev_tail,
-                        &r->ev_push_tail, &r->ev_step0, &r->ev_lane_start, &r->ev_lane_done};
+  std::vector<cudaEvent_t*> evs = {&r->ev_start, &r->ev_tail, &r->ev_push_tail, &r->ev_step0, &r->ev_lane_start, &r->ev_lane_done,
+                                   &r->ev_give_tail};
+  for (int i = 0; i < kSlots; ++i) {
+    evs.push_back(&r->ev_recv[i]);
+    evs.push_back(&r->ev_done[i]);
+    evs.push_back(&r->ev_part[i]);
+    evs.push_back(&r->ev_sent[i]);
+  }
   for (cudaEvent_t* ev : evs)
     if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess)
       return bail(fail_cuda(e, "cudaEventCreate"));
@@ -912,15 +931,20 @@ int ra_ring_destroy(ra_ring_t* r) {
   if (r->push_stream) cudaStreamSynchronize(r->push_stream);
   if (r->reduce_stream) cudaStreamSynchronize(r->reduce_stream);
   if (r->lane_stream) cudaStreamSynchronize(r->lane_stream);
+  if (r->give_stream) cudaStreamSynchronize(r->give_stream);
   if (r->p2p) close_peers(r);
   if (r->comm) {
     NcclApi* api = nccl_api();
     if (api) api->CommDestroy(r->comm);
   }
-  cudaEvent_t evs[] = {r->ev_start, r->ev_recv[0], r->ev_recv[1], r->ev_done[0], r->ev_done[1],
-                       r->ev_part[0], r->ev_part[1], r->ev_sent[0], r->ev_sent[1], r->ev_tail,
-                       r->ev_push_tail, r->ev_step0, r->ev_lane_start, r->ev_lane_done, r->t_begin[0], r->t_begin[1],
-                       r->t_end[0], r->t_end[1]};
+  std::vector<cudaEvent_t> evs = {r->ev_start, r->ev_tail, r->ev_push_tail, r->ev_step0, r->ev_lane_start, r->ev_lane_done,
+                                  r->ev_give_tail, r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
+  for (int i = 0; i < kSlots; ++i) {
+    evs.push_back(r->ev_recv[i]);
+    evs.push_back(r->ev_done[i]);
+    evs.push_back(r->ev_part[i]);
+    evs.push_back(r->ev_sent[i]);
+  }
   for (cudaEvent_t ev : evs)
     if (ev) cudaEventDestroy(ev);
   for (int d = 0; d < 2; ++d) {
@@ -931,9 +955,10 @@ int ra_ring_destroy(ra_ring_t* r) {
   if (r->push_stream) cudaStreamDestroy(r->push_stream);
   if (r->reduce_stream) cudaStreamDestroy(r->reduce_stream);
   if (r->lane_stream) cudaStreamDestroy(r->lane_stream);
+  if (r->give_stream) cudaStreamDestroy(r->give_stream);
   r->state.release();
   r->grads.release();
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < kSlots; ++i) {
     r->part[i].release();
     if (r->stage[i]) cudaFree(r->stage[i]);
     if (r->rpart[i]) cudaFree(r->rpart[i]);
@@ -1042,12 +1067,31 @@ int ra_ring_last_timing(ra_ring_t* r, int32_t backward, float* total_ms, float* 
   return 0;
 }
 
+int ra_ring_last_timeline(ra_ring_t* r, int32_t backward, int32_t max_items, float* blocks, int32_t* n_blocks,
+                          float* waits, int32_t* n_waits) {
+  if (!r) return fail(-30, "ring handle is NULL");
+  if (!r->timing) return fail(-35, "timing is off: call ra_ring_set_timing(ring, 1) first");
+  if (max_items < 0 || !blocks || !waits || !n_blocks || !n_waits) return fail(-6, "timeline: result pointers are NULL");
+  const int d = backward ? 1 : 0;
+  RA_CUDA(cudaEventSynchronize(r->t_end[d]), "cudaEventSynchronize");
+  std::vector<std::pair<float, float>> w, b;
+  int rc;
+  if ((rc = event_intervals(r->t_begin[d], r->t_events[d], r->t_used[d], &w))) return rc;
+  if ((rc = event_intervals(r->t_begin[d], r->b_events[d], r->b_used[d], &b))) return rc;
+  *n_blocks = (int32_t)std::min<size_t>(b.size(), (size_t)max_items);
+  *n_waits = (int32_t)std::min<size_t>(w.size(), (size_t)max_items);
+  for (int i = 0; i < *n_blocks; ++i) blocks[2 * i] = b[i].first, blocks[2 * i + 1] = b[i].second;
+  for (int i = 0; i < *n_waits; ++i) waits[2 * i] = w[i].first, waits[2 * i + 1] = w[i].second;
+  return 0;
+}
+
 int ra_ring_last_push(ra_ring_t* r, int32_t backward, double* bytes, float* push_ms) {
   if (!r) return fail(-30, "ring handle is NULL");
   if (!r->timing) return fail(-35, "timing is off: call ra_ring_set_timing(ring, 1) first");
   const int dir = backward ? 1 : 0;
   RA_CUDA(cudaEventSynchronize(r->t_end[dir]), "cudaEventSynchronize");
   if (r->push_stream) RA_CUDA(cudaStreamSynchronize(r->push_stream), "cudaStreamSynchronize");
+  if (r->give_stream) RA_CUDA(cudaStreamSynchronize(r->give_stream), "cudaStreamSynchronize");
   float sum = 0.f;
   for (size_t i = 0; i + 1 < r->p_used[dir]; i += 2) {
     float ms = 0.f;
@@ -1146,7 +1190,7 @@ int ra_ring_fwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     p.m = st_m[ln];
     p.l = st_l[ln];
     if (t > 0) {
-      use_staged(msg, ring->stage[t & 1], &p.k, &p.v, &p.mod);
+      use_staged(msg, ring->stage[t % kSlots], &p.k, &p.v, &p.mod);
       if ((rc = wait_kv(ring, t, s))) return rc;
     }
     p.first = !used[ln];
@@ -1259,7 +1303,7 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
   float* own2_dv = (float*)(g + delta_b + dq_b + dk_b + dv_b + own2_dk_b);
   KvMessage msg = make_kv_message(shape, p.k, p.v, p.mod);
   if (N > 1) {
-    for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(dk_b + dv_b), "cudaMalloc(part)");
+    for (int i = 0; i < kSlots; ++i) RA_CUDA(ring->part[i].reserve(dk_b + dv_b), "cudaMalloc(part)");
     if ((rc = ensure_shared(ring, msg.total, dk_b + dv_b))) return rc;
   }
   if (ring->plan && ring->plan->nranks != ring->nranks)
@@ -1340,7 +1384,7 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       }
       continue;
     }
-    const int slot = t & 1;
+    const int slot = t % kSlots;
     const int owner = ((me - t) % N + N) % N, giver = (me + t) % N;
     // Under a plan: this rank computes (and gives) only where its queries see the block, and
     // receives only where the giver's queries see this rank's block.
@@ -1352,8 +1396,8 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
     if (compute) {
       use_staged(msg, ring->stage[slot], &p.k, &p.v, &p.mod);
       if ((rc = wait_kv(ring, t, s))) return rc;
-      // part[slot] was last sent two steps ago, by this lane
-      if (t >= 3) RA_CUDA(cudaStreamWaitEvent(s, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
+      // part[slot] was last sent kSlots steps ago
+      if (t > kSlots) RA_CUDA(cudaStreamWaitEvent(s, ring->ev_sent[slot], 0), "cudaStreamWaitEvent");
       // this step's contribution is built from nothing: the kernel stores instead of adding
       p.dk = (float*)ring->part[slot].ptr;
       p.dv = (float*)((char*)ring->part[slot].ptr + dk_b);
@@ -1364,21 +1408,23 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
       p.overwrite = 0;
     }
     if ((rc = step_done(ring, t, s))) return rc;
+    // the stream this step's contribution travels on
+    cudaStream_t xfer = ring->p2p ? ring->give_stream : ring->push_stream;
     if (compute) {
       RA_CUDA(cudaEventRecord(ring->ev_part[slot], s), "cudaEventRecord");
       // give it to the block's owner; take what another rank computed for this rank's block
-      RA_CUDA(cudaStreamWaitEvent(ring->push_stream, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
+      RA_CUDA(cudaStreamWaitEvent(xfer, ring->ev_part[slot], 0), "cudaStreamWaitEvent");
     }
     if (ring->p2p) {
       if (compute) {
-        // the owner's rpart[slot] is free once it has summed the contribution of step t-2
-        const uint64_t need = t >= 3 ? ring->epoch + t - 1 : ring->epoch;
-        if ((rc = launch_wait(ring, ring->push_stream, kFlagAdded + owner, need))) return rc;
-        if ((rc = push_mark(ring, ring->push_stream, 0))) return rc;
+        // the owner's rpart[slot] is free once it has summed the contribution of step t - kSlots
+        const uint64_t need = t > kSlots ? ring->epoch + t - kSlots + 1 : ring->epoch;
+        if ((rc = launch_wait(ring, xfer, kFlagAdded + owner, need))) return rc;
+        if ((rc = push_mark(ring, xfer, 0))) return rc;
         double sent = 0;
         if (whole(give_rows)) {
           RA_CUDA(cudaMemcpyAsync(ring->peers[owner].rpart[slot], ring->part[slot].ptr, dk_b + dv_b,
-                                  cudaMemcpyDeviceToDevice, ring->push_stream), "cudaMemcpyAsync(peer dK/dV)");
+                                  cudaMemcpyDeviceToDevice, xfer), "cudaMemcpyAsync(peer dK/dV)");
           sent = (double)(dk_b + dv_b);
         } else {  // only the key rows this rank's queries saw: one strided copy per run, dK and dV
           for (int k = 0; k < give_rows.n; ++k)
@@ -1387,14 +1433,14 @@ int ra_ring_bwd(ra_ring_t* ring, const ra_shape_t* shape, const ra_tensor_t* q,
               const size_t pitch = (size_t)shape->lk * d * 4, off = base + (size_t)give_rows.lo[k] * d * 4;
               const size_t width = (size_t)(give_rows.hi[k] - give_rows.lo[k]) * d * 4;
               RA_CUDA(cudaMemcpy2DAsync((char*)ring->peers[owner].rpart[slot] + off, pitch, (char*)ring->part[slot].ptr + off, pitch,
-                                        width, (size_t)shape->b * shape->h, cudaMemcpyDeviceToDevice, ring->push_stream),
+                                        width, (size_t)shape->b * shape->h, cudaMemcpyDeviceToDevice, xfer),
                       "cudaMemcpy2DAsync(peer dK/dV rows)");
               sent += (double)width * shape->b * shape->h;
             }
         }
-        if ((rc = push_mark(ring, ring->push_stream, sent))) return rc;
-        if ((rc = launch_set(ring, ring->push_stream, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
-        RA_CUDA(cudaEventRecord(ring->ev_sent[slot], ring->push_stream), "cudaEventRecord");
+        if ((rc = push_mark(ring, xfer, sent))) return rc;
+        if ((rc = launch_set(ring, xfer, owner, kFlagPartReady + slot, ring->epoch + t))) return rc;
+        RA_CUDA(cudaEventRecord(ring->ev_sent[slot], xfer), "cudaEventRecord");
       }
       // owner side, on the reduce stream
       if (receive && (rc = launch_wait(ring, ring->reduce_stream, kFlagPartReady + slot, ring->epoch + t))) return rc;
@@ -1500,7 +1546,7 @@ int ra_ring_reserve(ra_ring_t* ring, const ra_shape_t* shape, const ra_score_mod
   if (backward) {
     RA_CUDA(ring->grads.reserve(3 * z.delta_b + z.dq_b + z.dk_b + z.dv_b + z.own2_dk_b + z.own2_dv_b), "cudaMalloc(grads)");
     if (N > 1)
-      for (int i = 0; i < 2; ++i) RA_CUDA(ring->part[i].reserve(z.dk_b + z.dv_b), "cudaMalloc(part)");
+      for (int i = 0; i < kSlots; ++i) RA_CUDA(ring->part[i].reserve(z.dk_b + z.dv_b), "cudaMalloc(part)");
   }
   if (N > 1 && (rc = ensure_shared(ring, msg.total, backward ? z.dk_b + z.dv_b : 0))) return rc;
   // the block kernels take their tile summaries from a stream-ordered pool that keeps what it

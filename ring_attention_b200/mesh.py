@@ -83,6 +83,14 @@ class Ring:
         check(lib.ra_ring_last_block_ms(self.handle, int(backward), C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
+    def last_timeline(self, backward: bool, max_items: int = 64):
+        """([(begin, end)] of the block launches, [(begin, end)] of the waits for transfers), in ms
+        from the start of the last forward / backward ring call."""
+        b, w = (C.c_float * (2 * max_items))(), (C.c_float * (2 * max_items))()
+        nb, nw = C.c_int32(), C.c_int32()
+        check(lib.ra_ring_last_timeline(self.handle, int(backward), max_items, b, C.byref(nb), w, C.byref(nw)))
+        return ([(b[2 * i], b[2 * i + 1]) for i in range(nb.value)], [(w[2 * i], w[2 * i + 1]) for i in range(nw.value)])
+
     def last_push(self, backward: bool):
         """(bytes this rank pushed to peers, device ms of those copies) in the last forward / backward ring call."""
         nbytes, ms = C.c_double(), C.c_float()

@@ -22,6 +22,8 @@ import random
 
 import pytest
 
+SLOTS = 4  # staging slots, contribution buffers and receive buffers per rank (slot = step % SLOTS)
+
 
 class Event:
     def __init__(self):
@@ -33,10 +35,10 @@ class Rank:
     def __init__(self, me, n):
         self.me, self.n = me, n
         self.flags = {}  # (name, index) -> value, this rank's page
-        self.stage = [None, None]  # K/V staging slots: (owner, step, call)
-        self.rpart = [None, None]  # received contributions: (giver, step, call)
-        self.part = [None, None]  # own contribution buffers: (step, call) being built / sent
-        self.streams = {"main": [], "lane": [], "push": [], "reduce": []}
+        self.stage = [None] * SLOTS  # K/V staging slots: (owner, step, call)
+        self.rpart = [None] * SLOTS  # received contributions: (giver, step, call)
+        self.part = [None] * SLOTS  # own contribution buffers: (step, call) being built / sent
+        self.streams = {"main": [], "lane": [], "push": [], "give": [], "reduce": []}
         self.state = [None, None]  # forward state of each lane: (call, steps folded in)
         self.events = {}
         self.log = []
@@ -96,11 +98,12 @@ class Model:
 
     # ---- the schedule: mirrors send_kv / wait_kv / step_done / ra_ring_fwd / ra_ring_bwd ----
     def send_kv(self, me, t):
-        n, E, slot, call = self.n, self.epoch, t & 1, self.call
+        n, E, slot, call = self.n, self.epoch, t % SLOTS, self.call
         to = (me + t) % n
         if not self.needed(to, me):
             return
-        self.wait_flag(me, "push", f"PROGRESS{t & 1}", to, E + t - 1 if t >= 3 else E)
+        # the consumer's stage[slot] was last read by its step t - SLOTS (same lane: SLOTS is even)
+        self.wait_flag(me, "push", f"PROGRESS{t & 1}", to, E + t - SLOTS + 1 if t > SLOTS else E)
 
         def copy():
             old = self.ranks[to].stage[slot]
@@ -120,7 +123,7 @@ class Model:
         def run():
             rk = self.ranks[me]
             if t > 0:
-                assert rk.stage[t & 1] == (src, t, call), f"rank {me} step {t} ({kind}) reads {rk.stage[t & 1]}, wants {(src, t, call)}"
+                assert rk.stage[t % SLOTS] == (src, t, call), f"rank {me} step {t} ({kind}) reads {rk.stage[t % SLOTS]}, wants {(src, t, call)}"
             rk.log.append(("block", kind, t, call))
             return True
 
@@ -145,12 +148,15 @@ class Model:
         self.wait_event(me, "push", "ev_start")
         self.wait_event(me, "reduce", "ev_start")
         self.wait_event(me, "lane", "ev_start")
+        self.wait_event(me, "give", "ev_start")
 
     def end_call(self, me):
         # both lanes' counters end the call at epoch + n: the next call's first pushes wait for that
         self.set_flag(me, "main", -1, "PROGRESS0", me, self.epoch + self.n)
         self.record(me, "push", "ev_push_tail")
         self.wait_event(me, "main", "ev_push_tail")
+        self.record(me, "give", "ev_give_tail")
+        self.wait_event(me, "main", "ev_give_tail")
 
     def join_lane(self, me):
         self.set_flag(me, "lane", -1, "PROGRESS1", me, self.epoch + self.n)
@@ -169,7 +175,7 @@ class Model:
                     continue
                 ln = self.lane(t)
                 if t > 0:
-                    self.wait_flag(me, ln, "KV_READY", t & 1, E + t)
+                    self.wait_flag(me, ln, "KV_READY", t % SLOTS, E + t)
                 self.block(me, ln, t, "fwd")
 
                 def fold(me=me, t=t, call=self.call):
@@ -212,12 +218,12 @@ class Model:
                     self.record(me, "main", "ev_step0")
                     self.wait_event(me, "reduce", "ev_step0")
                     continue
-                slot = t & 1
+                slot = t % SLOTS
                 owner, giver = (me - t) % n, (me + t) % n
                 compute, receive = self.needed(me, owner), self.needed(giver, me)
                 if compute:
                     self.wait_flag(me, ln, "KV_READY", slot, E + t)
-                    if t >= 3:
+                    if t > SLOTS:
                         self.wait_event(me, ln, f"ev_sent{slot}")
 
                     def clear(slot=slot, t=t, rk=rk, me=me):
@@ -231,8 +237,10 @@ class Model:
                 self.step_done(me, t)
                 if compute:
                     self.record(me, ln, f"ev_part{slot}")
-                    self.wait_event(me, "push", f"ev_part{slot}")
-                    self.wait_flag(me, "push", "ADDED", owner, E + t - 1 if t >= 3 else E)
+                    # contributions travel on a stream of their own: a K/V block for a later step must
+                    # not queue behind a contribution that waits for its block kernel
+                    self.wait_event(me, "give", f"ev_part{slot}")
+                    self.wait_flag(me, "give", "ADDED", owner, E + t - SLOTS + 1 if t > SLOTS else E)
 
                     def give(slot=slot, t=t, owner=owner, rk=rk, me=me):
                         assert rk.part[slot] == (t, call, "built"), (me, rk.part[slot])
@@ -242,9 +250,9 @@ class Model:
                         rk.part[slot] = (t, call, "sent")
                         return True
 
-                    self.op(me, "push", give, f"push contribution to {owner}")
-                    self.set_flag(me, "push", owner, "PART_READY", slot, E + t)
-                    self.record(me, "push", f"ev_sent{slot}")
+                    self.op(me, "give", give, f"push contribution to {owner}")
+                    self.set_flag(me, "give", owner, "PART_READY", slot, E + t)
+                    self.record(me, "give", f"ev_sent{slot}")
                 if receive:
                     self.wait_flag(me, "reduce", "PART_READY", slot, E + t)
 
@@ -267,7 +275,7 @@ class Model:
 
     # ---- execution: any stream whose head operation can run, in random order ------------------
     def run(self, rng):
-        heads = [(r, s) for r in range(self.n) for s in ("main", "lane", "push", "reduce")]
+        heads = [(r, s) for r in range(self.n) for s in ("main", "lane", "push", "give", "reduce")]
         pos = {h: 0 for h in heads}
         while True:
             rng.shuffle(heads)
@@ -311,7 +319,7 @@ def _check(model, n, calls):
                 assert ("finished", call) in log
 
 
-@pytest.mark.parametrize("n", [2, 3, 4, 5, 8])
+@pytest.mark.parametrize("n", [2, 3, 4, 5, 8, 11])
 @pytest.mark.parametrize("plan", ["none", "dense", "sparse", "diagonal"])
 def test_protocol_runs_to_completion_under_random_interleavings(n, plan):
     calls = ["fwd", "bwd", "fwd", "fwd", "bwd", "bwd"]
