@@ -233,6 +233,11 @@ struct ra_ring {
   // NCCL transport it is the transfer stream itself (one communicator, one stream).
   cudaStream_t give_stream = nullptr;
   cudaEvent_t ev_give_tail = nullptr;
+  // PROGRESS counters are published from this high-priority stream, behind an event of the lane:
+  // a one-thread kernel on a lane itself queues behind the other lane's block kernel until that
+  // kernel's last wave, and the peers' pushes would start that much later.
+  cudaStream_t flag_stream = nullptr;
+  cudaEvent_t ev_main_end = nullptr;
   cudaEvent_t ev_lane_start = nullptr, ev_lane_done = nullptr;
   cudaEvent_t ev_start = nullptr, ev_recv[ringimpl::kSlots] = {}, ev_done[ringimpl::kSlots] = {};
   cudaEvent_t ev_part[ringimpl::kSlots] = {}, ev_sent[ringimpl::kSlots] = {}, ev_tail = nullptr;
@@ -771,9 +776,10 @@ int wait_kv(ra_ring_t* r, int t, cudaStream_t stream) {
 // After the block kernel of step t: tell the ranks that may want to overwrite the slot.
 int step_done(ra_ring_t* r, int t, cudaStream_t stream) {
   if (r->nranks == 1) return 0;
-  if (r->p2p) return launch_set(r, stream, -1, progress_flag(t & 1, r->rank), r->epoch + t + 1);
   RA_CUDA(cudaEventRecord(r->ev_done[t % kSlots], stream), "cudaEventRecord");
-  return 0;
+  if (!r->p2p) return 0;
+  RA_CUDA(cudaStreamWaitEvent(r->flag_stream, r->ev_done[t % kSlots], 0), "cudaStreamWaitEvent");
+  return launch_set(r, r->flag_stream, -1, progress_flag(t & 1, r->rank), r->epoch + t + 1);
 }
 
 int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
@@ -799,9 +805,12 @@ int begin_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
 int join_lane(ra_ring_t* ring, cudaStream_t stream) {
   if (ring->nranks == 1) return 0;
   int rc;
-  if (ring->p2p && (rc = launch_set(ring, ring->lane_stream, -1, progress_flag(1, ring->rank), ring->epoch + ring->nranks))) return rc;
   RA_CUDA(cudaEventRecord(ring->ev_lane_done, ring->lane_stream), "cudaEventRecord");
   RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_lane_done, 0), "cudaStreamWaitEvent");
+  if (ring->p2p) {
+    RA_CUDA(cudaStreamWaitEvent(ring->flag_stream, ring->ev_lane_done, 0), "cudaStreamWaitEvent");
+    if ((rc = launch_set(ring, ring->flag_stream, -1, progress_flag(1, ring->rank), ring->epoch + ring->nranks))) return rc;
+  }
   return 0;
 }
 
@@ -809,7 +818,11 @@ int end_call(ra_ring_t* ring, int dir, cudaStream_t stream) {
   if (ring->nranks > 1) {
     // both lanes' counters end the call at epoch + nranks: the next call's first pushes wait for that
     int rc;
-    if (ring->p2p && (rc = launch_set(ring, stream, -1, progress_flag(0, ring->rank), ring->epoch + ring->nranks))) return rc;
+    if (ring->p2p) {
+      RA_CUDA(cudaEventRecord(ring->ev_main_end, stream), "cudaEventRecord");
+      RA_CUDA(cudaStreamWaitEvent(ring->flag_stream, ring->ev_main_end, 0), "cudaStreamWaitEvent");
+      if ((rc = launch_set(ring, ring->flag_stream, -1, progress_flag(0, ring->rank), ring->epoch + ring->nranks))) return rc;
+    }
     // the pushes read the caller's tensors: they must be over before the caller may reuse them
     RA_CUDA(cudaEventRecord(ring->ev_push_tail, ring->push_stream), "cudaEventRecord");
     RA_CUDA(cudaStreamWaitEvent(stream, ring->ev_push_tail, 0), "cudaStreamWaitEvent");
@@ -881,10 +894,11 @@ int ra_ring_create(int32_t rank, int32_t nranks, const uint8_t nccl_id[RA_UNIQUE
   if ((e = cudaStreamCreateWithPriority(&r->push_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
       (e = cudaStreamCreateWithPriority(&r->reduce_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
       (e = cudaStreamCreateWithPriority(&r->lane_stream, cudaStreamNonBlocking, prio_low)) != cudaSuccess ||
-      (e = cudaStreamCreateWithPriority(&r->give_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess)
+      (e = cudaStreamCreateWithPriority(&r->give_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
+      (e = cudaStreamCreateWithPriority(&r->flag_stream, cudaStreamNonBlocking, prio_high)) != cudaSuccess)
     return bail(fail_cuda(e, "cudaStreamCreate"));
   std::vector<cudaEvent_t*> evs = {&r->ev_start, &r->ev_tail, &r->ev_push_tail, &r->ev_step0, &r->ev_lane_start, &r->ev_lane_done,
-                                   &r->ev_give_tail};
+                                   &r->ev_give_tail, &r->ev_main_end};
   for (int i = 0; i < kSlots; ++i) {
     evs.push_back(&r->ev_recv[i]);
     evs.push_back(&r->ev_done[i]);
@@ -932,13 +946,14 @@ int ra_ring_destroy(ra_ring_t* r) {
   if (r->reduce_stream) cudaStreamSynchronize(r->reduce_stream);
   if (r->lane_stream) cudaStreamSynchronize(r->lane_stream);
   if (r->give_stream) cudaStreamSynchronize(r->give_stream);
+  if (r->flag_stream) cudaStreamSynchronize(r->flag_stream);
   if (r->p2p) close_peers(r);
   if (r->comm) {
     NcclApi* api = nccl_api();
     if (api) api->CommDestroy(r->comm);
   }
   std::vector<cudaEvent_t> evs = {r->ev_start, r->ev_tail, r->ev_push_tail, r->ev_step0, r->ev_lane_start, r->ev_lane_done,
-                                  r->ev_give_tail, r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
+                                  r->ev_give_tail, r->ev_main_end, r->t_begin[0], r->t_begin[1], r->t_end[0], r->t_end[1]};
   for (int i = 0; i < kSlots; ++i) {
     evs.push_back(r->ev_recv[i]);
     evs.push_back(r->ev_done[i]);
@@ -956,6 +971,7 @@ int ra_ring_destroy(ra_ring_t* r) {
   if (r->reduce_stream) cudaStreamDestroy(r->reduce_stream);
   if (r->lane_stream) cudaStreamDestroy(r->lane_stream);
   if (r->give_stream) cudaStreamDestroy(r->give_stream);
+  if (r->flag_stream) cudaStreamDestroy(r->flag_stream);
   r->state.release();
   r->grads.release();
   for (int i = 0; i < kSlots; ++i) {

@@ -75,6 +75,19 @@ def test_reserved_ring_calls_allocate_nothing():
     free1, _ = torch.cuda.mem_get_info()
     assert free1 == free0, f"device memory in use grew by {free0 - free1} bytes inside reserved ring calls"
     assert ra.device_status() == 0
+    # the timing diagnostics of the last call: one block launch per direction on a ring of one,
+    # no waits for transfers, nothing pushed
+    ring.set_timing(True)
+    check(lib.ra_ring_fwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), C.byref(mod), tv(out), lse.data_ptr(), stream))
+    check(lib.ra_ring_bwd(ring.handle, C.byref(sh), tv(q), tv(k), tv(v), tv(out), lse.data_ptr(), tv(do), C.byref(mod),
+                          tv(dq), tv(dk), tv(dv), stream))
+    for back in (False, True):
+        blocks, waits = ring.last_timeline(back)
+        assert len(blocks) == 1 and waits == [] and blocks[0][1] > blocks[0][0] >= 0, (blocks, waits)
+        total, exposed = ring.last_timing(back)
+        assert total >= blocks[0][1] - blocks[0][0] > 0 and exposed == 0
+        assert abs(ring.last_block_ms(back)[0] - (blocks[0][1] - blocks[0][0])) < 1e-3
+        assert ring.last_push(back) == (0.0, 0.0)
     ref = torch.nn.functional.scaled_dot_product_attention(
         q.transpose(1, 2).float(), k.transpose(1, 2).float(), v.transpose(1, 2).float(), is_causal=True).transpose(1, 2)
     assert (out.float() - ref).abs().max() < 3e-2

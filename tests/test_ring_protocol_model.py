@@ -38,7 +38,7 @@ class Rank:
         self.stage = [None] * SLOTS  # K/V staging slots: (owner, step, call)
         self.rpart = [None] * SLOTS  # received contributions: (giver, step, call)
         self.part = [None] * SLOTS  # own contribution buffers: (step, call) being built / sent
-        self.streams = {"main": [], "lane": [], "push": [], "give": [], "reduce": []}
+        self.streams = {"main": [], "lane": [], "push": [], "give": [], "reduce": [], "flag": []}
         self.state = [None, None]  # forward state of each lane: (call, steps folded in)
         self.events = {}
         self.log = []
@@ -141,7 +141,11 @@ class Model:
             return True
 
         self.op(me, self.lane(t), run, f"step {t} done")
-        self.set_flag(me, self.lane(t), -1, f"PROGRESS{t & 1}", me, self.epoch + t + 1)
+        # published from a high-priority stream behind an event: a one-thread kernel on the lane
+        # itself would queue behind the other lane's block kernel until its last wave
+        self.record(me, self.lane(t), f"ev_done{t % SLOTS}")
+        self.wait_event(me, "flag", f"ev_done{t % SLOTS}")
+        self.set_flag(me, "flag", -1, f"PROGRESS{t & 1}", me, self.epoch + t + 1)
 
     def begin_call(self, me):
         self.record(me, "main", "ev_start")
@@ -152,16 +156,19 @@ class Model:
 
     def end_call(self, me):
         # both lanes' counters end the call at epoch + n: the next call's first pushes wait for that
-        self.set_flag(me, "main", -1, "PROGRESS0", me, self.epoch + self.n)
+        self.record(me, "main", "ev_main_end")
+        self.wait_event(me, "flag", "ev_main_end")
+        self.set_flag(me, "flag", -1, "PROGRESS0", me, self.epoch + self.n)
         self.record(me, "push", "ev_push_tail")
         self.wait_event(me, "main", "ev_push_tail")
         self.record(me, "give", "ev_give_tail")
         self.wait_event(me, "main", "ev_give_tail")
 
     def join_lane(self, me):
-        self.set_flag(me, "lane", -1, "PROGRESS1", me, self.epoch + self.n)
         self.record(me, "lane", "ev_lane_done")
         self.wait_event(me, "main", "ev_lane_done")
+        self.wait_event(me, "flag", "ev_lane_done")
+        self.set_flag(me, "flag", -1, "PROGRESS1", me, self.epoch + self.n)
 
     def forward(self):
         n, E = self.n, self.epoch
@@ -275,7 +282,7 @@ class Model:
 
     # ---- execution: any stream whose head operation can run, in random order ------------------
     def run(self, rng):
-        heads = [(r, s) for r in range(self.n) for s in ("main", "lane", "push", "give", "reduce")]
+        heads = [(r, s) for r in range(self.n) for s in ("main", "lane", "push", "give", "reduce", "flag")]
         pos = {h: 0 for h in heads}
         while True:
             rng.shuffle(heads)
