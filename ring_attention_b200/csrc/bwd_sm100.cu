@@ -43,12 +43,6 @@ constexpr int kBwdThreads = 320;
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr unsigned kProducerPollNs = 100;
-// Of every 16 column pairs of P^T, how many get their exponentials from the polynomial on the
-// FMA pipe (the others use ex2 on the special-function unit).
-#ifndef RA_BWD_POLY_PAIRS
-#define RA_BWD_POLY_PAIRS 0
-#endif
-constexpr int kBwdPolyPairs = RA_BWD_POLY_PAIRS;
 
 struct BwdTcParams {
   CUtensorMap map_q, map_k, map_v, map_do;
@@ -487,8 +481,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
           }
         } else {
           // A masked pair (-inf) gives exp2(-inf) = 0; the clamp in the row term keeps a row whose L
-          // is -inf from turning that into exp2(-inf + inf).  Column pairs: packed arithmetic, and the first
-          // kBwdPolyPairs of every 16 pairs take the exponential from the FMA-pipe polynomial.
+          // is -inf from turning that into exp2(-inf + inf).  Column pairs: packed arithmetic.
           const uint64_t sc2 = pack2(sc, sc);
 #pragma unroll
           for (int c4 = 0; c4 < 16; ++c4) {
@@ -499,14 +492,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
               const int c = c4 * 4 + e;
               const uint64_t nl2 = pack2(l4[e], l4[e + 1]);  // min(-L * log2(e), 1e30) of the two queries
               const uint64_t x2 = fma2(pack2(__uint_as_float(sv[c >> 5][c & 31]), __uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31])), sc2, nl2);
-              if (((c >> 1) & 15) < kBwdPolyPairs) {
-                exp2_poly2(x2, pf[c], pf[c + 1]);
-              } else {
-                float x0, x1;
-                unpack2(x2, x0, x1);
-                pf[c] = ex2(x0);
-                pf[c + 1] = ex2(x1);
-              }
+              float x0, x1;
+              unpack2(x2, x0, x1);
+              pf[c] = ex2(x0);
+              pf[c + 1] = ex2(x1);
             }
           }
         }
