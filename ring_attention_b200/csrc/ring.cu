@@ -1,21 +1,27 @@
 // Ring schedule: one process per GPU.  The forward follows ring_attention/ring.py:79-137
-// and the backward ring.py:160-211, with two changes that NVSwitch makes free:
+// and the backward ring.py:160-211, with these changes that NVSwitch makes free:
 //   * at step t a rank works on the K/V block of rank (rank - t) mod N, exactly the
 //     block the reference's hop-by-hop ppermute (ring.py:54) would have delivered, but
-//     the owner sends it straight to its consumer (no forwarding hop), into the half of
-//     a double buffer that the running block kernel is not reading;
+//     the owner sends it straight to its consumer (no forwarding hop), into one of four
+//     staging slots (slot = step mod 4);
 //   * in the backward K/V are fetched the same way, dQ stays at home, and the dK/dV
-//     contribution of a step goes straight to the block's owner, which adds it in fp32.
+//     contribution of a step goes straight to the block's owner, which adds it in fp32;
+//   * the block kernels of adjacent steps run on two compute lanes (the caller's stream and a
+//     second stream), so that the tail of one overlaps the head of the next: the forward keeps
+//     one carried state per lane and merges them at the end, the backward's steps share only
+//     the dQ accumulator, which is added to with reductions.
 // Two transports:
 //   p2p  (default): the owner PUSHES with copy-engine peer copies (cudaMemcpyAsync into the
-//         consumer's staging buffer, mapped through CUDA IPC) on a high-priority side stream:
-//         no SM is used, so the copy really runs under the block kernel.  Ordering between
-//         GPUs uses 64-bit sequence counters in each rank's flag page, written with release
-//         stores by small kernels after the copy and polled with acquire loads by small
-//         bounded-wait kernels on the stream that needs the data.
-//   nccl: grouped ncclSend / ncclRecv on the side stream (RA_TRANSPORT=nccl).  Its fixed cost
-//         per exchange (~0.4 ms measured at 8 GPUs) is too high for short ring steps.
-// Nothing here synchronises the host, except when staging buffers have to grow.
+//         consumer's staging slot, mapped through CUDA IPC) on high-priority side streams (one
+//         for K/V blocks, one for contributions): no SM is used, so the copy really runs under
+//         the block kernel.  Ordering between GPUs uses 64-bit sequence counters in each rank's
+//         flag page, written with release stores by small kernels after the copy and polled with
+//         acquire loads by small bounded-wait kernels on the stream that needs the data.
+//   nccl: grouped ncclSend / ncclRecv on the side stream (RA_TRANSPORT=nccl, or chosen by every
+//         rank together when some rank cannot map a peer).  Its fixed cost per exchange (~0.4 ms
+//         measured at 8 GPUs) is too high for short ring steps.
+// Nothing here synchronises the host, except when buffers have to grow (ra_ring_reserve does
+// that ahead of time).
 #include <dlfcn.h>
 #include <nccl.h>
 
