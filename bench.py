@@ -196,7 +196,7 @@ def cpu_baseline(w, nranks=4, budget_s=20.0):
 
 
 def cpu_config1():
-    """BASELINE.json's CPU-runnable configuration, timed for real (nothing extrapolated):
+    """The reference's CPU-runnable configuration, timed for real (nothing extrapolated):
     fp32 causal forward + backward, batch 1, 4 heads, 1024 tokens over 4 virtual ranks, head dim 64."""
     from threadpoolctl import threadpool_limits
 
@@ -236,7 +236,7 @@ def run_reference(args, w):
         "note": "reference JAX path unavailable on this box (jax not installed, no network); "
                 "this is the CPU restatement of its algorithm; every step times a bounded sample "
                 "(sample_seconds, measured) and ms_per_step is the workload's time extrapolated from it by "
-                "FLOP count, so it does not fit inside this run; config1_cpu is BASELINE.json's CPU-runnable "
+                "FLOP count, so it does not fit inside this run; config1_cpu is the reference's CPU-runnable "
                 "configuration timed for real",
     }
     print(json.dumps(line), flush=True)
