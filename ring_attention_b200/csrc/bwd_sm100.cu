@@ -39,7 +39,22 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kBwdThreads = 320;
+// 10 warps; with the drain warpgroup (head dim 128) 16: warps 8-11 move dQ^T out of TMEM, warps
+// 12-15 hold the producer, the MMA issuer and two idle warps (registers are re-divided between
+// whole warpgroups).
+constexpr int bwd_threads(bool drain) { return drain ? 512 : 320; }
+// Registers per thread after the re-division, with the drain warpgroup: every scheduler hosts two
+// compute warps, one drain warp and one of the others, 2 * 152 + 152 + 56 = 512 = 16384 / 32.
+constexpr int kRegsCompute = 152, kRegsDrain = 152, kRegsOther = 56;
+
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr unsigned kProducerPollNs = 100;
@@ -72,8 +87,10 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D>
-__global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_constant__ BwdTcParams P) {
+template <int D, bool DRAIN>
+__global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __grid_constant__ BwdTcParams P) {
+  static_assert(!DRAIN || D == 128, "the drain warpgroup serves the dQ^T form");
+  constexpr int PRODUCER_WARP = DRAIN ? 12 : 8, MMA_WARP = PRODUCER_WARP + 1;
   constexpr int TILE_BYTES = kTileRows * D * 2;
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = kTileRows * 128;
@@ -113,7 +130,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
-      uint32_t cnt = (i == P_READY || i == DS_READY || i == DQ_DRAINED) ? 256u : 1u;
+      uint32_t cnt = (i == P_READY || i == DS_READY) ? 256u : (i == DQ_DRAINED) ? (DRAIN ? 128u : 256u) : 1u;
       mbar_init(&bars[i], cnt);
     }
     *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;  // the swizzled tiles need a 1024-byte aligned base
@@ -167,7 +184,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
   Window win0;
   const int first_tile = next_active(win0, 0) & kTileIdx;
   const bool has_work = first_tile < P.n_q_tiles;
-  if (warp == 9 && has_work) {
+  if (warp == MMA_WARP && has_work) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -181,7 +198,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
 
   if (bad) {
     // fall through to the common exit
-  } else if (warp == 8) {
+  } else if (warp >= PRODUCER_WARP) {
+    // the producer warp and the MMA warp; with the drain warpgroup they and two idle warps form
+    // a warpgroup, which hands most of its registers to the others
+    if constexpr (DRAIN) reg_dec<kRegsOther>();
+    if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------ TMA producer
     // The whole warp walks the tile sequence (the scan is warp-wide); lane 0 polls and issues.
     if (lane == 0) {
@@ -258,7 +279,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         if (__shfl_sync(0xffffffffu, stop, 0)) break;
       }
     }
-  } else if (warp == 9) {
+    } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------ MMA issuer
     {
       // every lane runs this loop; one elected lane issues each instruction
@@ -370,8 +391,56 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         if (ok) tc_commit_warp(&bars[DKDV_FULL]);
       }
     }
+    }
+  } else if (DRAIN && warp >= 8) {
+    // ------------------------------------------------------------ dQ^T drain (warps 8-11)
+    if constexpr (DRAIN) {
+      reg_inc<kRegsDrain>();
+      // This thread owns head-dim index r of dQ^T; the 128 columns are the tile's queries.  The
+      // whole tile goes to registers and the TMEM columns back to the MMA warp at once; then 8
+      // rounds of 16 queries pass through 4 staging buffers, and the TMA unit adds each
+      // [16 queries][128 head-dim lanes] box (8 KB) to the fp32 accumulator rows.  One thread
+      // issues; few large reduce-adds, not many small ones: the TMA unit's rate of operations,
+      // not its bytes, is what small boxes ran into.
+      const int r = (warp & 3) * 32 + lane;
+      const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+      const int64_t qrow_base = ((int64_t)bb * p.h + hh) * p.lq;
+      const bool issuer = warp == 8 && lane == 0;
+      Window win = win0;
+      bool ok = true;
+      int i = first_tile;
+      for (int n = 0; i < P.n_q_tiles; ++n) {
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
+        tc_fence_after();
+        uint32_t dv[4][32];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tmem_ld32(tmem_dP + lane_off + 32 * j, dv[j]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bars[DQ_DRAINED]);
+        const int dq_row0 = (int)(qrow_base + (int64_t)i * kTileRows);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float* buf = sdQ + (j & 3) * (16 * 128);
+          if (issuer) bulk_wait_group_read<3>();  // the reduce issued four rounds ago has read this buffer
+          named_bar_sync(1, 128);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) buf[c * 128 + r] = __uint_as_float(dv[(j * 16 + c) >> 5][(j * 16 + c) & 31]);
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (issuer) {
+            tma_reduce_add_2d(&P.map_dq, buf, 0, dq_row0 + j * 16);
+            bulk_commit_group();
+          }
+        }
+        i = next_active(win, i + 1) & kTileIdx;
+      }
+      // the staging buffers must outlive the reduce-adds that read them
+      if (issuer) bulk_wait_group<0>();
+    }
   } else {
     // ------------------------------------------------------------ compute (warps 0-7)
+    if constexpr (DRAIN) reg_inc<kRegsCompute>();
     const int g = warp >> 2;                         // warpgroup: query columns [64g, 64g+64)
     const int r = (warp & 3) * 32 + lane;            // key row of this thread = TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -407,25 +476,40 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DP_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
         tc_fence_after();
         tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
-        tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
+        if constexpr (!DRAIN) tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
         tc_wait_ld();
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_FREE], (n & 1) ^ 1, abort_flag, P.status, kStBwdCompute)))) break;
         uint8_t* row_ptr = sdS + g * PANEL_BYTES + r * 128;
         const uint64_t scl2 = pack2(p.scale, p.scale);
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        // 8 query columns (one 16-byte chunk of this key row of dS^T) from 8 dP^T values
+        auto ds_chunk = [&](int ch, const uint32_t* dp) {
           const float4 da = Dls[ch * 2], db = Dls[ch * 2 + 1];  // -delta * scale of 8 queries
           const uint64_t dl2[4] = {pack2(da.x, da.y), pack2(da.z, da.w), pack2(db.x, db.y), pack2(db.z, db.w)};
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = ch * 8 + e * 2;
-            const uint64_t dp2 = pack2(__uint_as_float(sv[c >> 5][c & 31]), __uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]));
+            const uint64_t dp2 = pack2(__uint_as_float(dp[e * 2]), __uint_as_float(dp[e * 2 + 1]));
             float d0, d1;
             unpack2(mul2(pack2(pf[c], pf[c + 1]), fma2(dp2, scl2, dl2[e])), d0, d1);
             w[e] = pack_bf16(d0, d1);
           }
           *reinterpret_cast<uint4*>(row_ptr + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        };
+        if constexpr (DRAIN) {
+          // fewer registers per thread here: the second 32 columns are loaded once half of the
+          // first 32 (and the P^T values that went with them) are no longer needed
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) ds_chunk(ch, &sv[0][ch * 8]);
+          tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
+#pragma unroll
+          for (int ch = 2; ch < 4; ++ch) ds_chunk(ch, &sv[0][ch * 8]);
+          tc_wait_ld();
+#pragma unroll
+          for (int ch = 4; ch < 8; ++ch) ds_chunk(ch, &sv[1][(ch - 4) * 8]);
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) ds_chunk(ch, &sv[ch >> 2][(ch & 3) * 8]);
         }
         fence_proxy_async_smem();
         tc_fence_before();
@@ -511,7 +595,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
         tc_fence_before();
         mbar_arrive(&bars[P_READY]);
       }
-      if (have_prev) {
+      if (have_prev && !DRAIN) {
         // ---- dQ of tile k-1: rows are queries; add this warpgroup's half of the columns
         const int n = k - 1;
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
@@ -650,29 +734,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1) tc_bwd_kernel(const __grid_con
       for (int c = 0; c < HALF / 4; ++c) dk_row[c] = dv_row[c] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     // the staging buffers must outlive the reduce-adds that read them
-    if constexpr (D == 128) {
+    if constexpr (D == 128 && !DRAIN) {
       if ((warp & 3) == 0 && lane == 0) bulk_wait_group<0>();
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9 && has_work) {
+  if (warp == MMA_WARP && has_work) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
 }
 
-template <int D>
+template <int D, bool DRAIN>
 cudaError_t launch_bwd(const BwdTcParams& P, cudaStream_t s) {
   constexpr size_t kSmem = (D == 128 ? 5 : 6) * kTileRows * D * 2 + kTileRows * kTileRows * 2 +
                            (D == 128 ? 8 * 2 * 16 * 32 * 4 : 0) + 4 * kTileRows * 4 + NUM_BARS * 8 + 64;
   constexpr size_t kRequest = kSmem < 120 * 1024 ? 120 * 1024 : kSmem;  // one CTA per SM: it owns all of TMEM
-  auto kern = tc_bwd_kernel<D>;
+  auto kern = tc_bwd_kernel<D, DRAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRequest);
   if (e != cudaSuccess) return e;
-  kern<<<P.n_kv_tiles * P.p.b * P.p.h, kBwdThreads, kRequest, s>>>(P);
+  kern<<<P.n_kv_tiles * P.p.b * P.p.h, bwd_threads(DRAIN), kRequest, s>>>(P);
   count_launch();
   return cudaGetLastError();
 }
@@ -754,7 +838,13 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
     P.meta_q = mq;
     P.meta_kv = mk;
   }
-  if (e == cudaSuccess) e = p.dk_dim == 128 ? launch_bwd<128>(P, s) : launch_bwd<64>(P, s);
+  if (e == cudaSuccess) {
+    static const bool drain_wg = [] {
+      const char* v = getenv("RA_BWD_DRAIN_WG");
+      return !(v && v[0] == '0');
+    }();
+    e = p.dk_dim == 128 ? (drain_wg ? launch_bwd<128, true>(P, s) : launch_bwd<128, false>(P, s)) : launch_bwd<64, false>(P, s);
+  }
   if (meta) cudaFreeAsync(meta, s);  // stream-ordered: after the kernels above, also when one failed to launch
   if (terms) cudaFreeAsync(terms, s);
   return e;
