@@ -16,15 +16,20 @@
 //   dV  += P^T dO         (TS MMA: A from TMEM, B = dO read MN-major) -> TMEM [256,256+D)
 //   dK  += dS^T Q         (SS MMA: B = Q read MN-major)               -> TMEM [256+D,256+2D)
 //   dQ^T = K^T dS^T       (SS MMA: A = K read MN-major, B = dS^T tile read MN-major; head dim 128)
-//                          -> TMEM [128,256), over dP^T; lane = head-dim index.  Each compute
-//                             warpgroup copies 16 of its 64 queries x 128 head-dim lanes at a
-//                             time into a shared-memory buffer and hands it to the TMA unit,
-//                             which adds the 8 KB box to the fp32 accumulator (tiled bulk
-//                             reduce-add): the SM's load/store path, which the MMAs' operand
-//                             reads share, sees plain stores only.
-//                             (head dim 64 forms dQ = dS K instead and uses vector reductions.)
-// warps 0-7: compute (two warpgroups split the 128 query columns), warp 8: TMA producer,
-// warp 9: MMA issuer.
+//                          -> TMEM [128,256), over dP^T; lane = head-dim index.  A warpgroup of
+//                             its own takes the whole tile into registers, hands the columns
+//                             back, and adds the values to the fp32 accumulator with one
+//                             reduction per query column: a warp's instruction covers 128
+//                             contiguous bytes of a dQ row.
+//                             (head dim 64 forms dQ = dS K instead; the compute warps reduce it.)
+// Shared-memory bandwidth bounds this kernel: an SS MMA of 128 x 128 x 16 reads 8 KB of operands
+// in the 64 cycles its arithmetic takes, which is all of the 128 bytes per cycle that shared
+// memory delivers, so every other shared-memory access (TMA writes of Q and dO, the dS^T
+// stores, the per-row terms) lengthens the MMAs.  That is why dQ leaves through registers and
+// not through a shared-memory staging buffer.
+// Head dim 128: warps 0-7 compute (two warpgroups split the 128 query columns), warps 8-11 drain
+// dQ^T, warp 12 TMA producer, warp 13 MMA issuer, warps 14-15 idle (registers are re-divided
+// between whole warpgroups).  Head dim 64: warps 0-7 compute, warp 8 producer, warp 9 MMA issuer.
 // Grid: CTAs of a few (batch, head) pairs at a time, so that the Q / dO tiles and the dQ
 // accumulator rows that the resident CTAs stream stay in L2.
 #include <cstdio>
@@ -39,9 +44,7 @@ namespace {
 
 using namespace ptx;
 
-// 10 warps; with the drain warpgroup (head dim 128) 16: warps 8-11 move dQ^T out of TMEM, warps
-// 12-15 hold the producer, the MMA issuer and two idle warps (registers are re-divided between
-// whole warpgroups).
+// 10 warps; with the drain warpgroup (head dim 128) 16
 constexpr int bwd_threads(bool drain) { return drain ? 512 : 320; }
 // Registers per thread after the re-division, with the drain warpgroup: every scheduler hosts two
 // compute warps, one drain warp and one of the others, 2 * 152 + 152 + 56 = 512 = 16384 / 32.
@@ -61,7 +64,6 @@ constexpr unsigned kProducerPollNs = 100;
 
 struct BwdTcParams {
   CUtensorMap map_q, map_k, map_v, map_do;
-  CUtensorMap map_dq;  // fp32 [b*h*lq, 128], box {128, 16}: head dim 128 only
   BwdParams p;
   const TileMeta* meta_q;
   const TileMeta* meta_kv;
@@ -87,27 +89,22 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D, bool DRAIN>
-__global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __grid_constant__ BwdTcParams P) {
-  static_assert(!DRAIN || D == 128, "the drain warpgroup serves the dQ^T form");
+template <int D>
+__global__ void __launch_bounds__(bwd_threads(D == 128), 1) tc_bwd_kernel(const __grid_constant__ BwdTcParams P) {
+  constexpr bool DRAIN = D == 128;  // the drain warpgroup serves the dQ^T form
   constexpr int PRODUCER_WARP = DRAIN ? 12 : 8, MMA_WARP = PRODUCER_WARP + 1;
   constexpr int TILE_BYTES = kTileRows * D * 2;
   constexpr int PANELS = D / 64;
   constexpr int PANEL_BYTES = kTileRows * 128;
   constexpr int DS_BYTES = kTileRows * kTileRows * 2;
-  // Head dim 128 keeps one dO stage (a dO tile is free after dV of its query tile, three MMA
-  // groups before the next tile's dP^T needs the next one) and spends the 32 KB on the dQ
-  // staging buffers: 2 warpgroups x 2 buffers x [16 queries][128 head-dim lanes] fp32.
-  constexpr int DO_ST = D == 128 ? 1 : 2;
-  constexpr int DQ_STAGE_BYTES = D == 128 ? 8 * 2 * 16 * 32 * 4 : 0;
+  constexpr int DO_ST = 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE_BYTES;
   uint8_t* sQ = sV + TILE_BYTES;          // 2 stages
   uint8_t* sdO = sQ + 2 * TILE_BYTES;     // DO_ST stages
   uint8_t* sdS = sdO + DO_ST * TILE_BYTES;  // [128 key rows][128 query cols] bf16, 2 panels, 128B swizzle
-  float* sdQ = reinterpret_cast<float*>(sdS + DS_BYTES);
-  float* sL = reinterpret_cast<float*>(sdS + DS_BYTES + DQ_STAGE_BYTES);  // [2][128]
+  float* sL = reinterpret_cast<float*>(sdS + DS_BYTES);  // [2][128]
   float* sDelta = sL + 2 * kTileRows;                     // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * kTileRows);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
@@ -210,7 +207,6 @@ __global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __g
       prefetch_tensormap(&P.map_k);
       prefetch_tensormap(&P.map_v);
       prefetch_tensormap(&P.map_do);
-      if constexpr (D == 128) prefetch_tensormap(&P.map_dq);
     }
     Window wq = win0, wdo = win0;
     const int i = first_tile;
@@ -397,15 +393,11 @@ __global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __g
     if constexpr (DRAIN) {
       reg_inc<kRegsDrain>();
       // This thread owns head-dim index r of dQ^T; the 128 columns are the tile's queries.  The
-      // whole tile goes to registers and the TMEM columns back to the MMA warp at once; then 8
-      // rounds of 16 queries pass through 4 staging buffers, and the TMA unit adds each
-      // [16 queries][128 head-dim lanes] box (8 KB) to the fp32 accumulator rows.  One thread
-      // issues; few large reduce-adds, not many small ones: the TMA unit's rate of operations,
-      // not its bytes, is what small boxes ran into.
+      // whole tile goes to registers and the TMEM columns back to the MMA warp at once; then one
+      // reduction per query: the warp's 32 lanes cover 128 contiguous bytes of that dQ row.
       const int r = (warp & 3) * 32 + lane;
       const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
       const int64_t qrow_base = ((int64_t)bb * p.h + hh) * p.lq;
-      const bool issuer = warp == 8 && lane == 0;
       Window win = win0;
       bool ok = true;
       int i = first_tile;
@@ -418,25 +410,12 @@ __global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __g
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(&bars[DQ_DRAINED]);
-        const int dq_row0 = (int)(qrow_base + (int64_t)i * kTileRows);
+        float* base = p.dq + (qrow_base + (int64_t)i * kTileRows) * 128 + r;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float* buf = sdQ + (j & 3) * (16 * 128);
-          if (issuer) bulk_wait_group_read<3>();  // the reduce issued four rounds ago has read this buffer
-          named_bar_sync(1, 128);
-#pragma unroll
-          for (int c = 0; c < 16; ++c) buf[c * 128 + r] = __uint_as_float(dv[(j * 16 + c) >> 5][(j * 16 + c) & 31]);
-          fence_proxy_async_smem();
-          named_bar_sync(1, 128);
-          if (issuer) {
-            tma_reduce_add_2d(&P.map_dq, buf, 0, dq_row0 + j * 16);
-            bulk_commit_group();
-          }
-        }
+        for (int c = 0; c < 128; ++c)
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + c * 128), "f"(__uint_as_float(dv[c >> 5][c & 31])) : "memory");
         i = next_active(win, i + 1) & kTileIdx;
       }
-      // the staging buffers must outlive the reduce-adds that read them
-      if (issuer) bulk_wait_group<0>();
     }
   } else {
     // ------------------------------------------------------------ compute (warps 0-7)
@@ -595,43 +574,12 @@ __global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __g
         tc_fence_before();
         mbar_arrive(&bars[P_READY]);
       }
-      if (have_prev && !DRAIN) {
-        // ---- dQ of tile k-1: rows are queries; add this warpgroup's half of the columns
-        const int n = k - 1;
-        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
-        tc_fence_after();
-        if constexpr (D == 128) {
-          // dQ^T: this thread owns head-dim index r; columns are the tile's queries, this warpgroup's 64
-          tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
-          tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
-          tc_wait_ld();
-          // the values are in registers: hand the TMEM columns back first, so that dP^T of the
-          // next tile does not wait for what follows
-          tc_fence_before();
-          mbar_arrive(&bars[DQ_DRAINED]);
-          // 4 rounds of 16 queries through this warpgroup's two staging buffers; the TMA unit adds
-          // each [16 queries][128 head-dim lanes] box (8 KB) to the accumulator rows.  One thread
-          // of the warpgroup issues; few large reduce-adds, not many small ones: the TMA unit's
-          // rate of operations, not its bytes, is what the small boxes ran into.
-          float* stage = sdQ + g * (2 * 16 * 128);
-          const int dq_row0 = (int)(qrow_base + (int64_t)i_prev * kTileRows + g * 64);
-          const bool issuer = (warp & 3) == 0 && lane == 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float* buf = stage + (j & 1) * (16 * 128);
-            if (issuer) bulk_wait_group_read<1>();  // the reduce issued two rounds ago has read this buffer
-            named_bar_sync(1 + g, 128);
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-              buf[c * 128 + r] = __uint_as_float(sv[(j * 16 + c) >> 5][(j * 16 + c) & 31]);
-            fence_proxy_async_smem();
-            named_bar_sync(1 + g, 128);
-            if (issuer) {
-              tma_reduce_add_2d(&P.map_dq, buf, 0, dq_row0 + j * 16);
-              bulk_commit_group();
-            }
-          }
-        } else {
+      if constexpr (!DRAIN) {
+        if (have_prev) {
+          // ---- dQ of tile k-1 (head dim 64): rows are queries; add this warpgroup's half of the columns
+          const int n = k - 1;
+          if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_FULL], n & 1, abort_flag, P.status, kStBwdCompute)))) break;
+          tc_fence_after();
           constexpr int HALF = D / 2;
           float* dq_row = p.dq + (qrow_base + (int64_t)i_prev * kTileRows + r) * D + g * HALF;
           tmem_ld32(tmem_dP + lane_off + g * HALF, sv[0]);
@@ -733,10 +681,6 @@ __global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __g
 #pragma unroll 1
       for (int c = 0; c < HALF / 4; ++c) dk_row[c] = dv_row[c] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // the staging buffers must outlive the reduce-adds that read them
-    if constexpr (D == 128 && !DRAIN) {
-      if ((warp & 3) == 0 && lane == 0) bulk_wait_group<0>();
-    }
   }
 
   tc_fence_before();
@@ -748,15 +692,14 @@ __global__ void __launch_bounds__(bwd_threads(DRAIN), 1) tc_bwd_kernel(const __g
   }
 }
 
-template <int D, bool DRAIN>
+template <int D>
 cudaError_t launch_bwd(const BwdTcParams& P, cudaStream_t s) {
-  constexpr size_t kSmem = (D == 128 ? 5 : 6) * kTileRows * D * 2 + kTileRows * kTileRows * 2 +
-                           (D == 128 ? 8 * 2 * 16 * 32 * 4 : 0) + 4 * kTileRows * 4 + NUM_BARS * 8 + 64;
+  constexpr size_t kSmem = 6 * kTileRows * D * 2 + kTileRows * kTileRows * 2 + 4 * kTileRows * 4 + NUM_BARS * 8 + 64;
   constexpr size_t kRequest = kSmem < 120 * 1024 ? 120 * 1024 : kSmem;  // one CTA per SM: it owns all of TMEM
-  auto kern = tc_bwd_kernel<D, DRAIN>;
+  auto kern = tc_bwd_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRequest);
   if (e != cudaSuccess) return e;
-  kern<<<P.n_kv_tiles * P.p.b * P.p.h, bwd_threads(DRAIN), kRequest, s>>>(P);
+  kern<<<P.n_kv_tiles * P.p.b * P.p.h, bwd_threads(D == 128), kRequest, s>>>(P);
   count_launch();
   return cudaGetLastError();
 }
@@ -782,7 +725,6 @@ const char* tc_bwd_unsupported_reason(const BwdParams& p, int dtype) {
       (reinterpret_cast<uintptr_t>(p.dv) & 15))
     return "lse/delta/dq/dk/dv need 16-byte aligned bases";
   if (!(p.scale > 0.f)) return "sm_scale must be positive";
-  if ((int64_t)p.b * p.h * p.lq >= (int64_t)1 << 31) return "b * h * lq must stay below 2^31";
   if (p.dk_out.ptr && (!aligned16(p.dk_out) || !p.dv_out.ptr || !aligned16(p.dv_out)))
     return "dk/dv results need 16-byte aligned bases and strides";
   return nullptr;
@@ -799,9 +741,6 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
       !make_tile_map(&P.map_k, p.k, p.b, p.lk, p.h, p.dk_dim, kTileRows, &why) ||
       !make_tile_map(&P.map_v, p.v, p.b, p.lk, p.h, p.dv_dim, kTileRows, &why) ||
       !make_tile_map(&P.map_do, p.dout, p.b, p.lq, p.h, p.dv_dim, kTileRows, &why))
-    return cudaErrorNotSupported;
-  if (p.dk_dim == 128 &&
-      !make_f32_rows_map(&P.map_dq, p.dq, (int64_t)p.b * p.h * p.lq, 128, 128, 16, &why))
     return cudaErrorNotSupported;
   P.status = device_status_word();
   if (!P.status) return cudaErrorInvalidSymbol;
@@ -838,13 +777,7 @@ cudaError_t tc_bwd_block(const BwdParams& p, cudaStream_t s) {
     P.meta_q = mq;
     P.meta_kv = mk;
   }
-  if (e == cudaSuccess) {
-    static const bool drain_wg = [] {
-      const char* v = getenv("RA_BWD_DRAIN_WG");
-      return !(v && v[0] == '0');
-    }();
-    e = p.dk_dim == 128 ? (drain_wg ? launch_bwd<128, true>(P, s) : launch_bwd<128, false>(P, s)) : launch_bwd<64, false>(P, s);
-  }
+  if (e == cudaSuccess) e = p.dk_dim == 128 ? launch_bwd<128>(P, s) : launch_bwd<64>(P, s);
   if (meta) cudaFreeAsync(meta, s);  // stream-ordered: after the kernels above, also when one failed to launch
   if (terms) cudaFreeAsync(terms, s);
   return e;

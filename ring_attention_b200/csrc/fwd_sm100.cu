@@ -577,27 +577,6 @@ bool make_tile_map(CUtensorMap* map, const TensorView& t, int b, int len, int h,
   return true;
 }
 
-bool make_f32_rows_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int box_cols, int box_rows,
-                       const char** why) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) {
-    *why = "cuTensorMapEncodeTiled is not available from this driver";
-    return false;
-  }
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    *why = "the driver refused the tensor map of the fp32 accumulator";
-    return false;
-  }
-  return true;
-}
-
 cudaError_t launch_tile_meta(TileMeta* out, const int32_t* pos, const int32_t* seg, const uint8_t* pre, int b,
                              int len, cudaStream_t s) {
   const int n_tiles = len / kTileRows;

@@ -119,11 +119,6 @@ __device__ __noinline__ void fixup_scores_tmem(uint32_t taddr, int ncols, uint32
 bool make_tile_map(CUtensorMap* map, const TensorView& t, int b, int len, int h, int d, int box_rows,
                    const char** why);
 
-// Tensor map over a dense fp32 matrix [rows, cols] with box {box_cols, box_rows}, no swizzle: the
-// destination of the backward kernel's tiled reduce-adds.
-bool make_f32_rows_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int box_cols, int box_rows,
-                       const char** why);
-
 // Launches the kernel that fills TileMeta[b][n_tiles] for one side (q or kv).
 cudaError_t launch_tile_meta(TileMeta* out, const int32_t* pos, const int32_t* seg, const uint8_t* pre,
                              int b, int len, cudaStream_t s);
