@@ -24,9 +24,9 @@
 //                             (head dim 64 forms dQ = dS K instead; the compute warps reduce it.)
 // Shared-memory bandwidth bounds this kernel: an SS MMA of 128 x 128 x 16 reads 8 KB of operands
 // in the 64 cycles its arithmetic takes, which is all of the 128 bytes per cycle that shared
-// memory delivers, so every other shared-memory access (TMA writes of Q and dO, the dS^T
-// stores, the per-row terms) lengthens the MMAs.  That is why dQ leaves through registers and
-// not through a shared-memory staging buffer.
+// memory delivers, so every other access on that data path (TMA writes of Q and dO, the dS^T
+// stores, the loads of the per-row terms, global reductions) lengthens the MMAs.  That is why
+// dQ leaves through registers and not through a shared-memory staging buffer as well.
 // Head dim 128: warps 0-7 compute (two warpgroups split the 128 query columns), warps 8-11 drain
 // dQ^T, warp 12 TMA producer, warp 13 MMA issuer, warps 14-15 idle (registers are re-divided
 // between whole warpgroups).  Head dim 64: warps 0-7 compute, warp 8 producer, warp 9 MMA issuer.
