@@ -73,7 +73,7 @@ struct BwdTcParams {
 };
 
 enum Bar {
-  KV_FULL = 0, Q_FULL0, Q_FULL1, Q_EMPTY0, Q_EMPTY1, DO_FULL0, DO_FULL1, DO_EMPTY0, DO_EMPTY1, S_FULL, DP_FULL, P_READY, DS_READY, DS_FREE,
+  KV_FULL = 0, Q_FULL0, Q_FULL1, Q_EMPTY0, Q_EMPTY1, DO_FULL0, DO_FULL1, DO_EMPTY0, DO_EMPTY1, S_FULL, DP_FULL, P_READY, DS_READY,
   DQ_FULL, DQ_DRAINED, DKDV_FULL, NUM_BARS
 };
 
@@ -372,7 +372,6 @@ __global__ void __launch_bounds__(bwd_threads(D == 128), 1) tc_bwd_kernel(const 
                      (n > 0) || kk > 0);
           }
           tc_commit_warp(&bars[Q_EMPTY0 + s]);
-          tc_commit_warp(&bars[DS_FREE]);
           if (!has_next) break;
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DQ_DRAINED], par, abort_flag, P.status, kStBwdMma)))) break;
           if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DO_FULL0 + dsn], dphn, abort_flag, P.status, kStBwdMma)))) break;
@@ -457,7 +456,9 @@ __global__ void __launch_bounds__(bwd_threads(D == 128), 1) tc_bwd_kernel(const 
         tmem_ld32(tmem_dP + lane_off + g * 64, sv[0]);
         if constexpr (!DRAIN) tmem_ld32(tmem_dP + lane_off + g * 64 + 32, sv[1]);
         tc_wait_ld();
-        if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars[DS_FREE], (n & 1) ^ 1, abort_flag, P.status, kStBwdCompute)))) break;
+        // dS^T of the tile before may be overwritten now: dP^T of this tile was issued after the
+        // MMAs that read it (dQ, dK), the tensor pipe runs in issue order, and DP_FULL's commit
+        // covers everything issued before it
         uint8_t* row_ptr = sdS + g * PANEL_BYTES + r * 128;
         const uint64_t scl2 = pack2(p.scale, p.scale);
         // 8 query columns (one 16-byte chunk of this key row of dS^T) from 8 dP^T values
