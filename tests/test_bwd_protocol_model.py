@@ -251,9 +251,9 @@ def run(tiles, drain, seed, mutate=None, max_steps=200000):
         roles["drain"] = cta.drain_wg()
     units = {"pipe": cta.run_pipe(), "loads": cta.run_loads()}
     live = dict(roles)
-    idle_rounds = 0
     # speeds differ per run: in some runs a role or a unit is ten times slower than the others
     weight = {n: rng.choice([1, 1, 3, 10]) for n in list(roles) + list(units)}
+    stuck = set()  # roles and units that could not move since anything last moved
     for _ in range(max_steps):
         if not live:
             break
@@ -264,13 +264,13 @@ def run(tiles, drain, seed, mutate=None, max_steps=200000):
             state = next(gen)
         except StopIteration:
             del live[name]
-            idle_rounds = 0
+            stuck.clear()
             continue
         if state == "ran":
-            idle_rounds = 0
+            stuck.clear()
         else:
-            idle_rounds += 1
-            if idle_rounds > 50 * len(names):  # every role looked many times and none could move
+            stuck.add(name)
+            if stuck >= set(names):  # every role waits and both units are empty
                 raise AssertionError(f"deadlock: {sorted(live)} still waiting; "
                                      f"{ {n: (b.phase, b.pending) for n, b in cta.bar.items()} }")
     assert not live, f"did not finish: {sorted(live)}"
