@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "ring_attention_b200.h"
+#include "score_mod.h"
 
 namespace ra {
 
@@ -95,27 +96,11 @@ cudaError_t launch_strict_nan(int b, int h, int lq, int lk, int dk_dim, int dv_d
 
 void count_launch(int n = 1);
 
-// One (query, key) score after scaling: mask + bias exactly as the reference's bias_fn
-// variants would produce it (ring.py:386-408), -inf where the pair is masked.
+// Score-mod inputs of one token (a query row or a key row).
 struct ModRow {
   int32_t pos, seg;
   bool pre;
 };
-
-__device__ __forceinline__ float apply_mod(float s, uint32_t kinds, int32_t window, float slope,
-                                           int32_t qpos, int32_t qseg, bool qpre, int32_t kpos,
-                                           int32_t kseg, bool kpre) {
-  bool vis = true;
-  if (kinds & RA_MOD_SEGMENT) vis = vis && (qseg == kseg);
-  if (kinds & RA_MOD_CAUSAL) {
-    vis = vis && (kpos <= qpos);
-  } else if (kinds & RA_MOD_PREFIX) {
-    vis = vis && ((qpre && kpre) || (kpos <= qpos));
-  }
-  if (kinds & RA_MOD_WINDOW) vis = vis && ((qpos - kpos) < window);
-  if (kinds & RA_MOD_ALIBI) s -= slope * (float)(qpos - kpos);
-  return vis ? s : -INFINITY;
-}
 
 template <typename T>
 __device__ __forceinline__ float load_as_float(const T* p);

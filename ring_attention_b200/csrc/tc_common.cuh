@@ -11,38 +11,6 @@ namespace ra {
 constexpr int kTileRows = 128;     // rows of one q tile / one kv tile
 constexpr int kMaxTiles = 4096;    // most tiles one block (shard) may have along either axis
 
-// Range summary of the per-token score-mod arrays over one 128-token tile.
-struct TileMeta {
-  int32_t pos_min, pos_max, seg_min, seg_max;
-  int32_t pre_any, pre_all;
-  int32_t pos_contig;  // 1 when the tile's positions are pos[0], pos[0] + 1, ... (then pos[0] == pos_min)
-  int32_t pad1;
-};
-
-// 0: every pair of the tile pair is masked; 1: every pair is visible; 2: mixed.
-__device__ __forceinline__ int classify_tiles(uint32_t kinds, int32_t window, const TileMeta& q,
-                                              const TileMeta& k) {
-  bool skip = false, full = true;
-  if (kinds & RA_MOD_SEGMENT) {
-    if (q.seg_max < k.seg_min || k.seg_max < q.seg_min) skip = true;
-    if (!(q.seg_min == q.seg_max && k.seg_min == k.seg_max && q.seg_min == k.seg_min)) full = false;
-  }
-  const bool causal_none = k.pos_min > q.pos_max, causal_all = k.pos_max <= q.pos_min;
-  if (kinds & RA_MOD_CAUSAL) {
-    if (causal_none) skip = true;
-    if (!causal_all) full = false;
-  } else if (kinds & RA_MOD_PREFIX) {
-    const bool pre_none = !(q.pre_any && k.pre_any), pre_all = q.pre_all && k.pre_all;
-    if (causal_none && pre_none) skip = true;
-    if (!(causal_all || pre_all)) full = false;
-  }
-  if (kinds & RA_MOD_WINDOW) {
-    if ((long long)q.pos_min - (long long)k.pos_max >= (long long)window) skip = true;
-    if (!((long long)q.pos_max - (long long)k.pos_min < (long long)window)) full = false;
-  }
-  return skip ? 0 : (full ? 1 : 2);
-}
-
 constexpr uint32_t kMaskKinds = RA_MOD_CAUSAL | RA_MOD_SEGMENT | RA_MOD_PREFIX | RA_MOD_WINDOW;
 // Score-mods that read the tile summaries (ALiBi reads pos_contig to choose its in-loop form).
 constexpr uint32_t kMetaKinds = kMaskKinds | RA_MOD_ALIBI;
